@@ -1,0 +1,108 @@
+/*
+ * qspec_b200_seq.h -- C ABI of the sequence-mixer kernels (library qspec_b200/_C/libqspec_b200_seq.so).
+ *
+ * These kernels serve decoder designs whose weights are plain bfloat16 / float32 matrices (no int4 path): layer
+ * norms with a zero-centred weight, short causal convolutions over time with a per-sequence tail, per-head
+ * query/key norms, chunk-local sigmoid attention over a per-slot key/value cache, squared-ReLU and clamped-gated
+ * feed-forward activations, a softmax router with top-k choice, and mixture-of-experts feed-forward layers
+ * (token-per-CTA form for decoding, tensor-core grouped form for prompts). Dense matrix products between them are
+ * left to the vendor library.
+ *
+ * Conventions (as in qspec_b200.h): device pointers, contiguous row-major, `stream` is a cudaStream_t, `int`
+ * status with qspec_last_error(). `dtype` is the element type of activations and of the large weight matrices:
+ * QSPEC_DTYPE_BF16 or QSPEC_DTYPE_F32. The residual stream, norm / convolution / bias vectors, router weights,
+ * convolution tails and everything the kernels reduce or exponentiate are float32 in both modes.
+ *
+ * Token batch: a step is a flat list of `ntok` tokens; the tokens of one sequence ("segment") are contiguous and in
+ * ascending position. `meta` is int32 [5][ntok]:
+ *   row 0 slot       cache / state slot of the token's sequence
+ *   row 1 pos        position of the token in its sequence (from 0)
+ *   row 2 seg_begin  batch index of the first token of its segment
+ *   row 3 seg_end    batch index one past the last token of its segment
+ *   row 4 phase      which of the two convolution-tail buffers holds the state BEFORE this step (0 / 1)
+ */
+#ifndef QSPEC_B200_SEQ_H_
+#define QSPEC_B200_SEQ_H_
+
+#include "qspec_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QSPEC_DTYPE_F32   2
+#define QSPEC_SEQ_META_ROWS 5
+
+/* x[i, :] = float(table[ids[i], :]).  table [V, W] dtype; ids int32 [ntok]; x float32 [ntok, W]. */
+int qspec_seq_embed(const void* table, const int* ids, float* x, int ntok, int W, int V, int dtype, void* stream);
+
+/* Sublayer entry: close the previous sublayer and open the next one in one launch.
+ *   r_t   = x_in[t] + unit_rms(y_t) * (1 + post_w)        (y_t = sum of `y_parts` rows; skipped when y == NULL)
+ *   h_t   = unit_rms(r_t) * (1 + pre_w)
+ *   out_t = h_t + sum_j conv_w[:, j] * h_(t - taps + 1 + j)  (rows before the segment come from the tail; before
+ *                                                             position 0 they are zero; conv_w == NULL: out = h)
+ * unit_rms(v) = v / sqrt(mean(v^2) + eps), all in float32. x_out receives r (must not alias x_in when y != NULL);
+ * out == NULL stops after r. tail: float32 [2][slots][taps-1][W]; the step reads buffer `phase` and writes buffer
+ * `1 - phase` with the last taps-1 rows of h of every segment (older rows are carried over).
+ * y row p of token t is y + t * y_tok_stride + p * y_part_stride (elements); part weights y_w (float32
+ * [ntok, y_parts], NULL = ones) multiply each part before the sum. W <= 16384, taps <= 8. */
+int qspec_seq_norm_conv(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                        long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
+                        const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok,
+                        int W, float eps, int dtype, void* stream);
+
+/* In-place per-head norm of the query and key sections of a fused projection buffer:
+ * row t = [q (H x D) | k (G x D) | v ...] with leading dimension ld; head <- unit_rms(head) * w. */
+int qspec_seq_qk_norm(void* qkv, int ld, const float* q_w, const float* k_w, int ntok, int H, int G, int D, float eps,
+                      int dtype, void* stream);
+
+/* Chunk-local sigmoid attention. Query at position i sees keys j <= i with floor(j / size) == floor(i / size);
+ * weight = sigmoid(cap(score) + bias[h]), cap(s) = softcap * tanh(s / softcap) (softcap <= 0: none),
+ * score = scale * q.k; weights are not normalised. Keys at positions inside the token's segment are read from the
+ * projection buffer (already normalised), earlier ones from the cache: cache_k [slots, size, G, D],
+ * cache_v [slots, size, G, DV], row = position % size. out [ntok, H*DV]. */
+int qspec_seq_chunk_attention(const void* qkv, int ld, const void* cache_k, const void* cache_v, const float* bias,
+                              void* out, const int* meta, int ntok, int H, int G, int D, int DV, int size, float scale,
+                              float softcap, int dtype, void* stream);
+
+/* Appends the step's keys / values to the cache: only the tokens in the chunk of their segment's LAST token are
+ * written (earlier chunks can never be seen again). Runs after qspec_seq_chunk_attention of the same step. */
+int qspec_seq_cache_append(const void* qkv, int ld, void* cache_k, void* cache_v, const int* meta, int ntok, int H,
+                           int G, int D, int DV, int size, int dtype, void* stream);
+
+/* Prompt form of the same attention on the tensor cores (bfloat16 only): one CTA per (64-query tile, kv head). */
+int qspec_seq_chunk_attention_mma(const void* qkv, int ld, const void* cache_k, const void* cache_v, const float* bias,
+                                  void* out, const int* meta, int ntok, int H, int G, int D, int DV, int size,
+                                  float scale, float softcap, void* stream);
+int qspec_seq_chunk_attention_mma_supported(int H, int G, int D, int DV);
+
+/* a <- relu(a)^2, n elements. */
+int qspec_seq_relu2(void* a, long long n, int dtype, void* stream);
+
+/* Router: z = router_w h (float32), s = softmax(z) over all R outputs, choice = s + correction, the `top` largest
+ * choices (lowest index among equals) -> idx int32 [ntok, top], weight float32 [ntok, top] = s of the chosen.
+ * router_w float32 [R, W], correction float32 [R]. R <= 1024, top <= 32. */
+int qspec_moe_route(const void* h, const float* router_w, const float* correction, int* idx, float* weight, int ntok,
+                    int W, int R, int top, int dtype, void* stream);
+
+/* Expert feed-forward, one CTA per (token, choice): y = min(g, limit) * sigmoid(1.702 min(g, limit)) *
+ * (clamp(u, +-limit) + 1) with [g ; u] = gate_up[e] h, out = down[e] y. Choices e >= E are identity experts (out = h).
+ * gate_up [E, 2*F, W] (gate rows first), down [E, W, F]; out [ntok, top, W] (unweighted). */
+int qspec_moe_expert_tokens(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
+                            int W, int F, int E, int top, float limit, int dtype, void* stream);
+
+/* Grouped form for many tokens (bfloat16, tensor cores). Workspace layout is internal; bytes from the query. */
+size_t qspec_moe_grouped_workspace_bytes(int ntok, int top, int E, int F);
+int qspec_moe_expert_grouped(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
+                             int W, int F, int E, int top, float limit, void* workspace, size_t workspace_bytes,
+                             void* stream);
+int qspec_moe_expert_grouped_supported(int W, int F);
+
+/* Arg max per row of float32 / bfloat16 logits [rows, V] (lowest index among equal maxima): int64 out. */
+int qspec_seq_argmax_rows(const void* logits, int rows, int V, long long row_stride, long long* out_idx, int dtype,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* QSPEC_B200_SEQ_H_ */

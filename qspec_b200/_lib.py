@@ -102,7 +102,30 @@ SIGNATURES = {
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p]),
 }
 
+# libqspec_b200_seq.so (include/qspec_b200_seq.h): the sequence-mixer kernels
+c_ll = ctypes.c_longlong
+SEQ_LIB_PATH = os.environ.get("QSPEC_SEQ_LIB") or os.path.join(_HERE, "_C", "libqspec_b200_seq.so")
+DTYPE_F32 = 2
+SEQ_SIGNATURES = {
+    "qspec_last_error": (c_char_p, []),
+    "qspec_launch_count": (c_uint64, []),
+    "qspec_seq_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "qspec_seq_norm_conv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_qk_norm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_chunk_attention": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "qspec_seq_cache_append": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_int, c_void_p]),
+    "qspec_seq_relu2": (c_int, [c_void_p, c_ll, c_int, c_void_p]),
+    "qspec_moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "qspec_moe_expert_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        c_float, c_int, c_void_p]),
+    "qspec_seq_argmax_rows": (c_int, [c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_void_p]),
+}
+
 _lib = None
+_seq_lib = None
 
 
 class QSpecNativeError(RuntimeError):
@@ -126,11 +149,29 @@ def load() -> ctypes.CDLL:
     return lib
 
 
-def check(status: int, what: str) -> None:
+def load_seq() -> ctypes.CDLL:
+    """The sequence-mixer library; like `load`, no fallback."""
+    global _seq_lib
+    if _seq_lib is not None:
+        return _seq_lib
+    if not os.path.exists(SEQ_LIB_PATH):
+        raise ImportError(
+            f"{SEQ_LIB_PATH} is missing: build it with `python -m qspec_b200.build --seq` "
+            "(qspec_b200 has no CPU or PyTorch fallback for its kernels)")
+    lib = ctypes.CDLL(SEQ_LIB_PATH)
+    for name, (res, args) in SEQ_SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _seq_lib = lib
+    return lib
+
+
+def check(status: int, what: str, lib=None) -> None:
     """Status 1/2 (bad argument / unsupported shape) -> ValueError, anything else -> QSpecNativeError."""
     if status == QSPEC_OK:
         return
-    msg = load().qspec_last_error()
+    msg = (lib or load()).qspec_last_error()
     text = msg.decode() if msg else "?"
     if status in (1, 2):
         raise ValueError(f"{what}: {text} (status {status})")

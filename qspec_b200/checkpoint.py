@@ -282,3 +282,57 @@ def save_qspec_checkpoint(model, path: str, shards: int = 2) -> None:
     for i in range(shards):
         part = {k: sd[k].contiguous() for k in keys[i * per:(i + 1) * per]}
         save_file(part, os.path.join(path, f"model-{i + 1:05d}-of-{shards:05d}.safetensors"))
+
+
+# ---- plain safetensors files (models whose weights are stored unquantised) ------------------------------------------
+_ST_DTYPES = {"BF16": torch.bfloat16, "F16": torch.float16, "F32": torch.float32, "F64": torch.float64, "I32": torch.int32,
+              "I64": torch.int64, "I8": torch.int8, "U8": torch.uint8}
+
+
+def read_safetensors_file(path: str) -> Dict[str, torch.Tensor]:
+    """One safetensors file read without the safetensors package: 8-byte little-endian header length, a JSON header
+    (name -> dtype, shape, data_offsets), then the raw little-endian data. Returns CPU tensors."""
+    import json
+    import struct
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        data = f.read()
+    out: Dict[str, torch.Tensor] = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        dt = _ST_DTYPES.get(info["dtype"])
+        if dt is None:
+            raise ValueError(f"{path}: tensor {name} has unsupported dtype {info['dtype']}")
+        a, b = info["data_offsets"]
+        shape = tuple(info["shape"])
+        numel = 1
+        for s in shape:
+            numel *= s
+        if b - a != numel * torch.empty(0, dtype=dt).element_size():
+            raise ValueError(f"{path}: tensor {name} has {b - a} bytes for shape {shape}")
+        t = torch.frombuffer(bytearray(data[a:b]), dtype=dt) if numel else torch.empty(0, dtype=dt)
+        out[name] = t.reshape(shape)
+    return out
+
+
+def write_safetensors_file(path: str, tensors: Mapping[str, torch.Tensor]) -> None:
+    """Inverse of `read_safetensors_file` (tests and examples write small models with it)."""
+    import json
+    import struct
+    names = {v: k for k, v in _ST_DTYPES.items()}
+    header, blobs, at = {}, [], 0
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[name] = {"dtype": names[t.dtype], "shape": list(t.shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)

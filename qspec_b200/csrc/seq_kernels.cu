@@ -1,0 +1,561 @@
+// Sequence-mixer kernels (include/qspec_b200_seq.h): norms with a zero-centred weight fused with the residual sum and a
+// short causal convolution over time, per-head query/key norms, chunk-local sigmoid attention over a per-slot cache,
+// router and expert feed-forward in the token-per-CTA form. Templated on the element type of activations and large
+// weights (bfloat16 / float32); every reduction, exponential and the residual stream are float32 in both.
+#include "common.cuh"
+#include "../../include/qspec_b200_seq.h"
+
+namespace qspec {
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+struct TokMeta {
+  int slot, pos, seg_begin, seg_end, phase;
+};
+__device__ __forceinline__ TokMeta load_meta(const int* meta, int ntok, int i) {
+  TokMeta m;
+  m.slot = meta[i];
+  m.pos = meta[ntok + i];
+  m.seg_begin = meta[2 * ntok + i];
+  m.seg_end = meta[3 * ntok + i];
+  m.phase = meta[4 * ntok + i];
+  return m;
+}
+
+// ---- embedding ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) embed_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
+                                                    int W, int V) {
+  pdl_enter();
+  const int i = blockIdx.x;
+  int id = ids[i];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const T* row = table + (size_t)id * W;
+  for (int c = threadIdx.x; c < W; c += 256) x[(size_t)i * W + c] = to_f(row[c]);
+}
+
+// ---- residual + post-norm + pre-norm + short convolution ------------------------------------------------------
+// One CTA per token. The convolution needs the normalised rows of the previous taps-1 tokens: rows inside the step's
+// segment are recomputed from their inputs (two reductions per row; the rows are L2-resident), rows before it come from
+// the per-slot tail. Shared memory: taps rows of W floats.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_conv_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const T* __restrict__ y, int y_parts,
+                 long long y_part_stride, long long y_tok_stride, const float* __restrict__ y_w,
+                 const float* __restrict__ post_w, const float* __restrict__ pre_w, const float* __restrict__ conv_w,
+                 int taps, float* __restrict__ tail, int slots, T* __restrict__ out, const int* __restrict__ meta, int ntok,
+                 int W, float eps) {
+  pdl_enter();
+  extern __shared__ float sm_rows[];          // [taps][W]
+  __shared__ float red[8];
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const TokMeta m = load_meta(meta, ntok, i);
+  const int pos_start = m.pos - (i - m.seg_begin);
+  const int hist = taps - 1;
+  const size_t tail_buf = (size_t)slots * hist * W;
+  const float* tail_rd = tail ? tail + (size_t)m.phase * tail_buf + (size_t)m.slot * hist * W : nullptr;
+  float* tail_wr = tail ? tail + (size_t)(1 - m.phase) * tail_buf + (size_t)m.slot * hist * W : nullptr;
+  const float inv_w = 1.0f / (float)W;
+  const int rows = (conv_w && out) ? taps : 1;
+
+  for (int j = 0; j < rows; ++j) {
+    float* hrow = sm_rows + (size_t)j * W;
+    const int u = i - j;
+    if (u >= m.seg_begin) {
+      const float* xr = x_in + (size_t)u * W;
+      if (y) {
+        float ss = 0.f;
+        for (int c = tid; c < W; c += 256) {
+          float v = 0.f;
+          for (int p = 0; p < y_parts; ++p) {
+            const float e = to_f(y[(size_t)u * y_tok_stride + (size_t)p * y_part_stride + c]);
+            v += y_w ? y_w[(size_t)u * y_parts + p] * e : e;
+          }
+          hrow[c] = v;
+          ss += v * v;
+        }
+        const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
+        for (int c = tid; c < W; c += 256) {
+          const float v = xr[c] + hrow[c] * r * (1.0f + post_w[c]);
+          hrow[c] = v;
+          if (j == 0) x_out[(size_t)i * W + c] = v;
+        }
+      } else {
+        for (int c = tid; c < W; c += 256) {
+          const float v = xr[c];
+          hrow[c] = v;
+          if (j == 0 && x_out != x_in && x_out) x_out[(size_t)i * W + c] = v;
+        }
+      }
+      if (!out) return;
+      float ss = 0.f;
+      for (int c = tid; c < W; c += 256) ss += hrow[c] * hrow[c];
+      const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
+      for (int c = tid; c < W; c += 256) hrow[c] = hrow[c] * r * (1.0f + pre_w[c]);
+    } else {
+      const int pu = m.pos - j;                               // position of the wanted row, before the segment
+      const int r = pu - (pos_start - hist);                  // its row in the tail
+      for (int c = tid; c < W; c += 256) hrow[c] = (pu >= 0 && tail_rd) ? tail_rd[(size_t)r * W + c] : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int c = tid; c < W; c += 256) {
+    float v = sm_rows[c];
+    if (conv_w) {
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) acc += conv_w[(size_t)c * taps + (taps - 1 - j)] * sm_rows[(size_t)j * W + c];
+      v += acc;
+    }
+    out[(size_t)i * W + c] = from_f<T>(v);
+  }
+  if (!tail_wr || hist == 0) return;
+  // new tail row r holds position pos_end - hist + r
+  const int pos_end = pos_start + (m.seg_end - m.seg_begin);
+  const int my_row = m.pos - (pos_end - hist);
+  if (my_row >= 0)
+    for (int c = tid; c < W; c += 256) tail_wr[(size_t)my_row * W + c] = sm_rows[c];
+  if (i == m.seg_begin) {                                     // rows older than the segment are carried over
+    for (int r = 0; r < hist; ++r) {
+      const int p = pos_end - hist + r;
+      if (p >= pos_start) break;
+      const int ro = p - (pos_start - hist);
+      for (int c = tid; c < W; c += 256) tail_wr[(size_t)r * W + c] = p >= 0 ? tail_rd[(size_t)ro * W + c] : 0.f;
+    }
+  }
+}
+
+// ---- per-head query / key norm ----------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+qk_norm_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_w, const float* __restrict__ k_w, int ntok, int H,
+               int G, int D, float eps) {
+  pdl_enter();
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= (long long)ntok * (H + G)) return;
+  const int t = (int)(row / (H + G)), hd = (int)(row % (H + G));
+  T* p = qkv + (size_t)t * ld + (size_t)hd * D;               // key heads follow the query heads in the row
+  const float* w = hd < H ? q_w : k_w;
+  float ss = 0.f;
+  for (int c = lane; c < D; c += 32) {
+    const float v = to_f(p[c]);
+    ss += v * v;
+  }
+  ss = warp_xor_sum(ss);
+  const float r = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int c = lane; c < D; c += 32) p[c] = from_f<T>(to_f(p[c]) * r * w[c]);
+}
+
+// ---- chunk-local sigmoid attention, one CTA per (token, query head) ------------------------------------------------
+__device__ __forceinline__ float capped_sigmoid_weight(float dot, float scale, float softcap, float bias) {
+  float s = dot * scale;
+  if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+  return 1.0f / (1.0f + expf(-(s + bias)));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+chunk_attn_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ ck, const T* __restrict__ cv,
+                  const float* __restrict__ bias, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G,
+                  int D, int DV, int size, float scale, float softcap) {
+  pdl_enter();
+  extern __shared__ float sm_att[];           // q [D] | weights [size]
+  float* sq = sm_att;
+  float* sw = sm_att + D;
+  const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int g = h / (H / G);
+  const TokMeta m = load_meta(meta, ntok, i);
+  const int pos_start = m.pos - (i - m.seg_begin);
+  const int lo = (m.pos / size) * size;
+  const int nkeys = m.pos - lo + 1;
+  const int koff = H * D + g * D, voff = H * D + G * D + g * DV;
+  const T* qp = qkv + (size_t)i * ld + (size_t)h * D;
+  for (int c = tid; c < D; c += 128) sq[c] = to_f(qp[c]);
+  __syncthreads();
+  const float b = bias[h];
+  for (int jj = tid; jj < nkeys; jj += 128) {
+    const int pj = lo + jj;
+    const T* kp = pj >= pos_start ? qkv + (size_t)(m.seg_begin + pj - pos_start) * ld + koff
+                                  : ck + (((size_t)m.slot * size + jj) * G + g) * D;
+    float dot = 0.f;
+    for (int c = 0; c < D; ++c) dot += sq[c] * to_f(kp[c]);
+    sw[jj] = capped_sigmoid_weight(dot, scale, softcap, b);
+  }
+  __syncthreads();
+  for (int d = tid; d < DV; d += 128) {
+    float acc = 0.f;
+    for (int jj = 0; jj < nkeys; ++jj) {
+      const int pj = lo + jj;
+      const T* vp = pj >= pos_start ? qkv + (size_t)(m.seg_begin + pj - pos_start) * ld + voff
+                                    : cv + (((size_t)m.slot * size + jj) * G + g) * DV;
+      acc += sw[jj] * to_f(vp[d]);
+    }
+    out[(size_t)i * H * DV + (size_t)h * DV + d] = from_f<T>(acc);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+cache_append_kernel(const T* __restrict__ qkv, int ld, T* __restrict__ ck, T* __restrict__ cv, const int* __restrict__ meta,
+                    int ntok, int H, int G, int D, int DV, int size) {
+  pdl_enter();
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const TokMeta m = load_meta(meta, ntok, i);
+  const int pos_start = m.pos - (i - m.seg_begin);
+  const int last = pos_start + (m.seg_end - m.seg_begin) - 1;
+  if (m.pos < (last / size) * size) return;
+  const int row = m.pos % size;
+  const T* kp = qkv + (size_t)i * ld + (size_t)H * D;
+  const T* vp = kp + (size_t)G * D;
+  T* kd = ck + ((size_t)m.slot * size + row) * G * D;
+  T* vd = cv + ((size_t)m.slot * size + row) * G * DV;
+  for (int c = tid; c < G * D; c += 128) kd[c] = kp[c];
+  for (int c = tid; c < G * DV; c += 128) vd[c] = vp[c];
+}
+
+// ---- feed-forward pieces ----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) relu2_kernel(T* __restrict__ a, long long n) {
+  pdl_enter();
+  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
+    const float v = fmaxf(to_f(a[k]), 0.f);
+    a[k] = from_f<T>(v * v);
+  }
+}
+
+// Router: one CTA of 128 threads per token. Dot products by warp, then softmax and top-k by one warp.
+template <typename T>
+__global__ void __launch_bounds__(128)
+route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float* __restrict__ corr, int* __restrict__ idx,
+             float* __restrict__ weight, int W, int R, int top) {
+  pdl_enter();
+  extern __shared__ float sm_rt[];            // z [R] | choice [R]
+  float* z = sm_rt;
+  float* ch = sm_rt + R;
+  const int i = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* hp = h + (size_t)i * W;
+  for (int r = warp; r < R; r += 4) {
+    const float* wr = rw + (size_t)r * W;
+    float acc = 0.f;
+    for (int c = lane; c < W; c += 32) acc += wr[c] * to_f(hp[c]);
+    acc = warp_xor_sum(acc);
+    if (lane == 0) z[r] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mx = -INFINITY;
+  for (int r = lane; r < R; r += 32) mx = fmaxf(mx, z[r]);
+  mx = warp_xor_max(mx);
+  float sum = 0.f;
+  for (int r = lane; r < R; r += 32) {
+    const float e = expf(z[r] - mx);
+    z[r] = e;
+    sum += e;
+  }
+  sum = warp_xor_sum(sum);
+  for (int r = lane; r < R; r += 32) {
+    z[r] = z[r] / sum;
+    ch[r] = z[r] + corr[r];
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int r = lane; r < R; r += 32)
+      if (ch[r] > bv) { bv = ch[r]; bi = r; }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (bi >= R) bi = 0;                                      // NaN scores: still a valid index
+    if (lane == 0) {
+      idx[(size_t)i * top + k] = bi;
+      weight[(size_t)i * top + k] = z[bi];
+      ch[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+// Expert feed-forward for few tokens: one CTA per (token, choice); a warp per output row, lanes along the reduction
+// (coalesced weight rows, each read once per CTA).
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_tokens_kernel(const T* __restrict__ h, const T* __restrict__ gate_up, const T* __restrict__ down,
+                     const int* __restrict__ idx, T* __restrict__ out, int W, int F, int E, int top, float limit) {
+  pdl_enter();
+  extern __shared__ float sm_ex[];            // h [W] | y [F]
+  float* sh = sm_ex;
+  float* sy = sm_ex + W;
+  const int i = blockIdx.x, k = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int e = idx[(size_t)i * top + k];
+  const T* hp = h + (size_t)i * W;
+  T* op = out + ((size_t)i * top + k) * W;
+  if (e >= E || e < 0) {
+    for (int c = tid; c < W; c += 256) op[c] = hp[c];
+    return;
+  }
+  for (int c = tid; c < W; c += 256) sh[c] = to_f(hp[c]);
+  __syncthreads();
+  const T* wg = gate_up + (size_t)e * 2 * F * W;
+  const T* wu = wg + (size_t)F * W;
+  for (int f = warp; f < F; f += 8) {
+    float ag = 0.f, au = 0.f;
+    for (int c = lane; c < W; c += 32) {
+      ag += to_f(wg[(size_t)f * W + c]) * sh[c];
+      au += to_f(wu[(size_t)f * W + c]) * sh[c];
+    }
+    ag = warp_xor_sum(ag);
+    au = warp_xor_sum(au);
+    if (lane == 0) {
+      // the projections leave the matrix unit in the activation type
+      const float gq = fminf(to_f(from_f<T>(ag)), limit);
+      const float uq = fminf(fmaxf(to_f(from_f<T>(au)), -limit), limit);
+      sy[f] = to_f(from_f<T>(gq * (1.0f / (1.0f + expf(-1.702f * gq))) * (uq + 1.0f)));
+    }
+  }
+  __syncthreads();
+  const T* wd = down + (size_t)e * W * F;
+  for (int c = warp; c < W; c += 8) {
+    float acc = 0.f;
+    for (int f = lane; f < F; f += 32) acc += to_f(wd[(size_t)c * F + f]) * sy[f];
+    acc = warp_xor_sum(acc);
+    if (lane == 0) op[c] = from_f<T>(acc);
+  }
+}
+
+// ---- greedy sampling over float32 / bfloat16 logits -----------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_rows_any_kernel(const T* __restrict__ logits, int V, long long ld, long long* __restrict__ out_idx) {
+  pdl_enter();
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T* x = logits + (size_t)blockIdx.x * ld;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = tid; c < V; c += 256) {
+    const float v = to_f(x[c]);
+    if (v > bv) { bv = v; bi = c; }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+    out_idx[blockIdx.x] = bi < V ? bi : 0;
+  }
+}
+
+}  // namespace qspec
+
+using namespace qspec;
+
+#define SEQ_DTYPE_OK(dtype) QSPEC_REQUIRE((dtype) == QSPEC_DTYPE_BF16 || (dtype) == QSPEC_DTYPE_F32, QSPEC_ERR_UNSUPPORTED, \
+                                          "dtype %d: bfloat16 (1) or float32 (2) expected", (dtype))
+
+extern "C" int qspec_seq_embed(const void* table, const int* ids, float* x, int ntok, int W, int V, int dtype, void* stream) {
+  QSPEC_REQUIRE(table && ids && x, QSPEC_ERR_INVALID_ARG, "seq_embed: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && V > 0, QSPEC_ERR_INVALID_ARG, "seq_embed: bad sizes");
+  SEQ_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(embed_kernel<float>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const float*)table, ids, x, W, V);
+  else
+    launch_pdl(embed_kernel<__nv_bfloat16>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)table, ids, x, W, V);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+template <typename T>
+static int launch_norm_conv(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                            long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
+                            const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok, int W,
+                            float eps, cudaStream_t st) {
+  const size_t smem = (size_t)taps * W * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(norm_conv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  launch_pdl(norm_conv_kernel<T>, dim3(ntok), dim3(256), smem, st, x_in, x_out, (const T*)y, y_parts, y_part_stride, y_tok_stride,
+             y_w, post_w, pre_w, conv_w, taps, tail, slots, (T*)out, meta, ntok, W, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_norm_conv(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                                   long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
+                                   const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok,
+                                   int W, float eps, int dtype, void* stream) {
+  QSPEC_REQUIRE(x_in && meta, QSPEC_ERR_INVALID_ARG, "seq_norm_conv: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && W <= 16384, QSPEC_ERR_UNSUPPORTED, "seq_norm_conv: width %d (1..16384)", W);
+  QSPEC_REQUIRE(!y || (x_out && x_out != x_in && post_w && y_parts >= 1), QSPEC_ERR_INVALID_ARG,
+                "seq_norm_conv: a pending sublayer output needs its norm weight and a separate x_out");
+  QSPEC_REQUIRE(!out || pre_w, QSPEC_ERR_INVALID_ARG, "seq_norm_conv: out without a norm weight");
+  QSPEC_REQUIRE(out || y, QSPEC_ERR_INVALID_ARG, "seq_norm_conv: nothing to do");
+  if (!conv_w) taps = 1;
+  QSPEC_REQUIRE(taps >= 1 && taps <= 8, QSPEC_ERR_UNSUPPORTED, "seq_norm_conv: %d taps (1..8)", taps);
+  QSPEC_REQUIRE(!conv_w || taps == 1 || (tail && slots > 0), QSPEC_ERR_INVALID_ARG, "seq_norm_conv: convolution without a tail buffer");
+  SEQ_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  if (!conv_w) tail = nullptr;
+  if (dtype == QSPEC_DTYPE_F32)
+    return launch_norm_conv<float>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps, tail,
+                                   slots, out, meta, ntok, W, eps, (cudaStream_t)stream);
+  return launch_norm_conv<__nv_bfloat16>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps,
+                                         tail, slots, out, meta, ntok, W, eps, (cudaStream_t)stream);
+}
+
+extern "C" int qspec_seq_qk_norm(void* qkv, int ld, const float* q_w, const float* k_w, int ntok, int H, int G, int D, float eps,
+                                 int dtype, void* stream) {
+  QSPEC_REQUIRE(qkv && q_w && k_w, QSPEC_ERR_INVALID_ARG, "seq_qk_norm: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && H > 0 && G > 0 && D > 0 && ld >= (H + G) * D, QSPEC_ERR_INVALID_ARG, "seq_qk_norm: bad sizes");
+  SEQ_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  const long long rows = (long long)ntok * (H + G);
+  const dim3 grid((unsigned)((rows + 3) / 4));
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(qk_norm_kernel<float>, grid, dim3(128), 0, (cudaStream_t)stream, (float*)qkv, ld, q_w, k_w, ntok, H, G, D, eps);
+  else
+    launch_pdl(qk_norm_kernel<__nv_bfloat16>, grid, dim3(128), 0, (cudaStream_t)stream, (__nv_bfloat16*)qkv, ld, q_w, k_w, ntok, H, G,
+               D, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+static int check_attn_args(const void* qkv, int ld, const void* ck, const void* cv, const int* meta, int ntok, int H, int G, int D,
+                           int DV, int size, const char* what) {
+  QSPEC_REQUIRE(qkv && ck && cv && meta, QSPEC_ERR_INVALID_ARG, "%s: null pointer", what);
+  QSPEC_REQUIRE(ntok >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && DV > 0 && size > 0, QSPEC_ERR_INVALID_ARG,
+                "%s: bad sizes (H %d, G %d, D %d, DV %d, chunk %d)", what, H, G, D, DV, size);
+  QSPEC_REQUIRE(ld >= H * D + G * D + G * DV, QSPEC_ERR_INVALID_ARG, "%s: leading dimension %d too small", what, ld);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_chunk_attention(const void* qkv, int ld, const void* cache_k, const void* cache_v, const float* bias,
+                                         void* out, const int* meta, int ntok, int H, int G, int D, int DV, int size, float scale,
+                                         float softcap, int dtype, void* stream) {
+  if (int s = check_attn_args(qkv, ld, cache_k, cache_v, meta, ntok, H, G, D, DV, size, "seq_chunk_attention")) return s;
+  QSPEC_REQUIRE(bias && out, QSPEC_ERR_INVALID_ARG, "seq_chunk_attention: null pointer");
+  SEQ_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  const size_t smem = (size_t)(D + size) * sizeof(float);
+  QSPEC_REQUIRE(smem <= 200 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_chunk_attention: chunk of %d keys does not fit shared memory", size);
+  static size_t configured[2] = {0, 0};
+  const int w = dtype == QSPEC_DTYPE_F32 ? 0 : 1;
+  if (smem > 48 * 1024 && smem > configured[w]) {
+    if (w == 0) QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    else QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[w] = smem;
+  }
+  if (w == 0)
+    launch_pdl(chunk_attn_kernel<float>, dim3(ntok, H), dim3(128), smem, (cudaStream_t)stream, (const float*)qkv, ld,
+               (const float*)cache_k, (const float*)cache_v, bias, (float*)out, meta, ntok, H, G, D, DV, size, scale, softcap);
+  else
+    launch_pdl(chunk_attn_kernel<__nv_bfloat16>, dim3(ntok, H), dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, ld,
+               (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, bias, (__nv_bfloat16*)out, meta, ntok, H, G, D, DV, size,
+               scale, softcap);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_cache_append(const void* qkv, int ld, void* cache_k, void* cache_v, const int* meta, int ntok, int H, int G,
+                                      int D, int DV, int size, int dtype, void* stream) {
+  if (int s = check_attn_args(qkv, ld, cache_k, cache_v, meta, ntok, H, G, D, DV, size, "seq_cache_append")) return s;
+  SEQ_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(cache_append_kernel<float>, dim3(ntok), dim3(128), 0, (cudaStream_t)stream, (const float*)qkv, ld, (float*)cache_k,
+               (float*)cache_v, meta, ntok, H, G, D, DV, size);
+  else
+    launch_pdl(cache_append_kernel<__nv_bfloat16>, dim3(ntok), dim3(128), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, ld,
+               (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, meta, ntok, H, G, D, DV, size);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_relu2(void* a, long long n, int dtype, void* stream) {
+  QSPEC_REQUIRE(a && n >= 0, QSPEC_ERR_INVALID_ARG, "seq_relu2: bad arguments");
+  SEQ_DTYPE_OK(dtype);
+  if (n == 0) return QSPEC_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(relu2_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (float*)a, n);
+  else
+    launch_pdl(relu2_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (__nv_bfloat16*)a, n);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_moe_route(const void* h, const float* router_w, const float* correction, int* idx, float* weight, int ntok, int W,
+                               int R, int top, int dtype, void* stream) {
+  QSPEC_REQUIRE(h && router_w && correction && idx && weight, QSPEC_ERR_INVALID_ARG, "moe_route: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && R > 0 && R <= 1024 && top >= 1 && top <= 32 && top <= R, QSPEC_ERR_UNSUPPORTED,
+                "moe_route: %d router outputs (<= 1024), top %d (<= 32)", R, top);
+  SEQ_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  const size_t smem = (size_t)2 * R * sizeof(float);
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(route_kernel<float>, dim3(ntok), dim3(128), smem, (cudaStream_t)stream, (const float*)h, router_w, correction, idx,
+               weight, W, R, top);
+  else
+    launch_pdl(route_kernel<__nv_bfloat16>, dim3(ntok), dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)h, router_w,
+               correction, idx, weight, W, R, top);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_moe_expert_tokens(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok, int W,
+                                       int F, int E, int top, float limit, int dtype, void* stream) {
+  QSPEC_REQUIRE(h && idx && out && (E == 0 || (gate_up && down)), QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && F >= 0 && E >= 0 && top >= 1 && top <= 65535, QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: bad sizes");
+  SEQ_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  const size_t smem = (size_t)(W + F) * sizeof(float);
+  QSPEC_REQUIRE(smem <= 200 * 1024, QSPEC_ERR_UNSUPPORTED, "moe_expert_tokens: width %d + expert size %d exceed shared memory", W, F);
+  static size_t configured[2] = {0, 0};
+  const int w = dtype == QSPEC_DTYPE_F32 ? 0 : 1;
+  if (smem > 48 * 1024 && smem > configured[w]) {
+    if (w == 0) QSPEC_CUDA(cudaFuncSetAttribute(expert_tokens_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    else QSPEC_CUDA(cudaFuncSetAttribute(expert_tokens_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[w] = smem;
+  }
+  if (w == 0)
+    launch_pdl(expert_tokens_kernel<float>, dim3(ntok, top), dim3(256), smem, (cudaStream_t)stream, (const float*)h,
+               (const float*)gate_up, (const float*)down, idx, (float*)out, W, F, E, top, limit);
+  else
+    launch_pdl(expert_tokens_kernel<__nv_bfloat16>, dim3(ntok, top), dim3(256), smem, (cudaStream_t)stream, (const __nv_bfloat16*)h,
+               (const __nv_bfloat16*)gate_up, (const __nv_bfloat16*)down, idx, (__nv_bfloat16*)out, W, F, E, top, limit);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_argmax_rows(const void* logits, int rows, int V, long long row_stride, long long* out_idx, int dtype,
+                                     void* stream) {
+  QSPEC_REQUIRE(logits && out_idx, QSPEC_ERR_INVALID_ARG, "seq_argmax_rows: null pointer");
+  QSPEC_REQUIRE(rows >= 0 && V > 0 && row_stride >= V, QSPEC_ERR_INVALID_ARG, "seq_argmax_rows: bad sizes");
+  SEQ_DTYPE_OK(dtype);
+  if (rows == 0) return QSPEC_OK;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(argmax_rows_any_kernel<float>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const float*)logits, V, row_stride, out_idx);
+  else
+    launch_pdl(argmax_rows_any_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)logits, V,
+               row_stride, out_idx);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}

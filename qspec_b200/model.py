@@ -352,6 +352,32 @@ class QSpecLlamaModel(torch.nn.Module):
             pending = True
         yield from staged(pending, lambda: self._norm_f16(nrm, x, out_m if pending else None, 1, sp_m))   # final norm is always fp16 (:533)
 
+    # ---- what `scheduler.Scheduler` drives (plain decoding through the verify-mode path) ---------------------------
+    @property
+    def n_slots(self) -> int:
+        return self.cache_k.shape[1]
+
+    @property
+    def max_step_tokens(self) -> int:
+        return self.max_tokens
+
+    @property
+    def vocab_size(self) -> int:
+        return self.cfg.vocab_size
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.cfg.max_seq_len
+
+    def forward_batch(self, input_ids: torch.Tensor, meta) -> torch.Tensor:
+        """A flat token batch described by a `state.BatchMeta` (slot and position per token) in W4A16 mode."""
+        return self.forward(input_ids.to(torch.int64), meta.pos.contiguous(), meta.slot.contiguous(), w4a4=False)
+
+    def logits(self, hidden_rows: torch.Tensor) -> torch.Tensor:
+        if self.tp_size != 1:
+            raise NotImplementedError("full logits of a vocab-sharded lm_head: use greedy_tokens")
+        return torch.matmul(hidden_rows, self.lm_head.t())
+
     def _norm_f16(self, nrm, x, delta, which=0, sp=None):
         if delta is None:
             ops.rms_norm_general_fuse_sum_fp16(nrm, x, self.cfg.rms_norm_eps)

@@ -685,15 +685,23 @@ def attn_block(qkv: torch.Tensor, cos_sin_cache: torch.Tensor, positions: torch.
 
 
 def argmax_rows(logits: torch.Tensor, out_val: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Greedy token per row of the f16 logits [rows, V]: int64 indices (lowest index among equal maxima, like
+    """Greedy token per row of the logits [rows, V] (float16; bfloat16 / float32 through the sequence-mixer library): int64 indices (lowest index among equal maxima, like
     torch.argmax on distinct values); out_val (f32 [rows], optional) receives the maxima."""
-    if not logits.is_cuda or logits.dtype != _F16:
-        raise ValueError("argmax_rows: logits must be a float16 CUDA tensor (qspec_b200 has no CPU path)")
+    if not logits.is_cuda or logits.dtype not in (_F16, _BF16, torch.float32):
+        raise ValueError("argmax_rows: logits must be a float16 / bfloat16 / float32 CUDA tensor (qspec_b200 has no CPU path)")
     if logits.dim() != 2 or logits.stride(1) != 1:
         raise ValueError("argmax_rows: logits must be [rows, V] with unit column stride")
     rows, V = logits.shape
     out = torch.empty(rows, dtype=torch.int64, device=logits.device)
     if rows == 0:
+        return out
+    if logits.dtype != _F16:                       # bfloat16 / float32 logits: the sequence-mixer library's kernel
+        if out_val is not None:
+            raise ValueError("argmax_rows: out_val is only available for float16 logits")
+        seq = _lib.load_seq()
+        _lib.check(seq.qspec_seq_argmax_rows(_ptr(logits), rows, V, logits.stride(0), _ptr(out),
+                                             _lib.DTYPE_BF16 if logits.dtype == _BF16 else _lib.DTYPE_F32, _stream()),
+                   "argmax_rows", seq)
         return out
     lib = _lib.load()
     ws = _workspace("argmax", lib.qspec_argmax_rows_workspace_bytes(rows), logits.device)
@@ -724,3 +732,129 @@ def tp_argmax_combine(local_max: torch.Tensor, local_idx: torch.Tensor, index_of
 
 def launch_count() -> int:
     return int(_lib.load().qspec_launch_count())
+
+
+# ---------------------------------------------------------------------------------------------
+# Sequence-mixer kernels (include/qspec_b200_seq.h, libqspec_b200_seq.so): bfloat16 / float32
+# activations and weights, float32 residual stream. No counterpart in the reference.
+# ---------------------------------------------------------------------------------------------
+_F32 = torch.float32
+_SEQ_ACT = (_BF16, _F32)
+
+
+def _sdt(t: torch.Tensor) -> int:
+    if t.dtype == _BF16:
+        return _lib.DTYPE_BF16
+    if t.dtype == _F32:
+        return _lib.DTYPE_F32
+    raise ValueError(f"expected bfloat16 or float32 tensor, got {t.dtype}")
+
+
+def _seq(status: int, what: str) -> None:
+    _lib.check(status, what, _lib.load_seq())
+
+
+def seq_launch_count() -> int:
+    return int(_lib.load_seq().qspec_launch_count())
+
+
+def seq_embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
+    """x[i] = float32(table[ids[i]]); ids int32 [ntok], x float32 [ntok, W]."""
+    _chk(table, "table", _SEQ_ACT); _chk(ids, "ids", (torch.int32,)); _chk(x, "x", (_F32,))
+    V, W = table.shape
+    if x.shape != (ids.numel(), W):
+        raise ValueError("seq_embed: x must be [ntok, W]")
+    _seq(_lib.load_seq().qspec_seq_embed(_ptr(table), _ptr(ids), _ptr(x), ids.numel(), W, V, _sdt(table), _stream()), "seq_embed")
+
+
+def seq_norm_conv(x_in: torch.Tensor, meta: torch.Tensor, eps: float, *, out: Optional[torch.Tensor] = None,
+                  pre_w: Optional[torch.Tensor] = None, conv_w: Optional[torch.Tensor] = None,
+                  tail: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None, y_w: Optional[torch.Tensor] = None,
+                  post_w: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None) -> None:
+    """Closes a sublayer (x_out = x_in + zero-centred norm of y, with weight post_w) and opens the next
+    (out = h + causal short convolution of h, h = zero-centred norm of the new residual with weight pre_w) in one launch.
+    y: [ntok, W] or [ntok, parts, W] (parts summed, each times y_w [ntok, parts] if given). tail: float32
+    [2, slots, taps-1, W], read at meta's phase, written at the other. out None: only the residual sum."""
+    _chk(x_in, "x_in", (_F32,)); _chk(meta, "meta", (torch.int32,))
+    ntok, W = x_in.shape
+    if meta.shape != (5, ntok):
+        raise ValueError("seq_norm_conv: meta must be int32 [5, ntok]")
+    for t, n in ((pre_w, "pre_w"), (conv_w, "conv_w"), (tail, "tail"), (y_w, "y_w"), (post_w, "post_w"), (x_out, "x_out")):
+        _chk(t, n, (_F32,), allow_none=True)
+    _chk(out, "out", _SEQ_ACT, allow_none=True); _chk(y, "y", _SEQ_ACT, allow_none=True)
+    parts, pstride, tstride = 1, 0, W
+    if y is not None:
+        if y.dim() == 3:
+            parts, pstride, tstride = y.shape[1], W, y.shape[1] * W
+        if y.shape[0] != ntok or y.shape[-1] != W or (y_w is not None and y_w.shape != (ntok, parts)):
+            raise ValueError("seq_norm_conv: y / y_w shapes do not match x")
+    taps = conv_w.shape[1] if conv_w is not None else 1
+    slots = 0
+    if conv_w is not None and taps > 1:
+        if tail is None or tail.dim() != 4 or tail.shape[0] != 2 or tail.shape[2] != taps - 1 or tail.shape[3] != W:
+            raise ValueError("seq_norm_conv: tail must be float32 [2, slots, taps-1, W]")
+        slots = tail.shape[1]
+    act = out if out is not None else y
+    _seq(_lib.load_seq().qspec_seq_norm_conv(_ptr(x_in), _ptr(x_out), _ptr(y), parts, pstride, tstride, _ptr(y_w), _ptr(post_w),
+                                             _ptr(pre_w), _ptr(conv_w), taps, _ptr(tail), slots, _ptr(out), _ptr(meta), ntok, W,
+                                             float(eps), _sdt(act), _stream()), "seq_norm_conv")
+
+
+def seq_qk_norm(qkv: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, H: int, G: int, D: int, eps: float) -> None:
+    """In place: every query and key head of the fused projection rows [q | k | v] <- head / rms(head) * w."""
+    _chk(qkv, "qkv", _SEQ_ACT); _chk(q_w, "q_w", (_F32,)); _chk(k_w, "k_w", (_F32,))
+    _seq(_lib.load_seq().qspec_seq_qk_norm(_ptr(qkv), qkv.shape[1], _ptr(q_w), _ptr(k_w), qkv.shape[0], H, G, D, float(eps),
+                                           _sdt(qkv), _stream()), "seq_qk_norm")
+
+
+def seq_chunk_attention(qkv: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, bias: torch.Tensor, out: torch.Tensor,
+                        meta: torch.Tensor, H: int, G: int, D: int, DV: int, size: int, scale: float, softcap: float) -> None:
+    """Chunk-local sigmoid attention of a token batch; cache_k [slots, size, G, D], cache_v [slots, size, G, DV]."""
+    for t, n in ((qkv, "qkv"), (cache_k, "cache_k"), (cache_v, "cache_v"), (out, "out")):
+        _chk(t, n, (qkv.dtype,))
+    _chk(qkv, "qkv", _SEQ_ACT); _chk(bias, "bias", (_F32,)); _chk(meta, "meta", (torch.int32,))
+    ntok = qkv.shape[0]
+    if out.shape != (ntok, H * DV) or meta.shape != (5, ntok) or cache_k.shape[1:] != (size, G, D) or cache_v.shape[1:] != (size, G, DV):
+        raise ValueError("seq_chunk_attention: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_chunk_attention(_ptr(qkv), qkv.shape[1], _ptr(cache_k), _ptr(cache_v), _ptr(bias), _ptr(out),
+                                                   _ptr(meta), ntok, H, G, D, DV, size, float(scale), float(softcap or 0.0),
+                                                   _sdt(qkv), _stream()), "seq_chunk_attention")
+
+
+def seq_cache_append(qkv: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, meta: torch.Tensor, H: int, G: int, D: int,
+                     DV: int, size: int) -> None:
+    """Writes the step's keys / values of every segment's last chunk into the cache (after the step's attention)."""
+    for t, n in ((qkv, "qkv"), (cache_k, "cache_k"), (cache_v, "cache_v")):
+        _chk(t, n, (qkv.dtype,))
+    _seq(_lib.load_seq().qspec_seq_cache_append(_ptr(qkv), qkv.shape[1], _ptr(cache_k), _ptr(cache_v), _ptr(meta), qkv.shape[0], H, G,
+                                                D, DV, size, _sdt(qkv), _stream()), "seq_cache_append")
+
+
+def seq_relu2(a: torch.Tensor) -> None:
+    _chk(a, "a", _SEQ_ACT)
+    _seq(_lib.load_seq().qspec_seq_relu2(_ptr(a), a.numel(), _sdt(a), _stream()), "seq_relu2")
+
+
+def moe_route(h: torch.Tensor, router_w: torch.Tensor, correction: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor) -> None:
+    """Softmax router with a choice correction: idx int32 [ntok, top], weight float32 [ntok, top] (plain scores)."""
+    _chk(h, "h", _SEQ_ACT); _chk(router_w, "router_w", (_F32,)); _chk(correction, "correction", (_F32,))
+    _chk(idx, "idx", (torch.int32,)); _chk(weight, "weight", (_F32,))
+    ntok, W = h.shape
+    R, top = router_w.shape[0], idx.shape[1]
+    if router_w.shape[1] != W or correction.numel() != R or idx.shape != (ntok, top) or weight.shape != (ntok, top):
+        raise ValueError("moe_route: shapes do not match")
+    _seq(_lib.load_seq().qspec_moe_route(_ptr(h), _ptr(router_w), _ptr(correction), _ptr(idx), _ptr(weight), ntok, W, R, top, _sdt(h),
+                                         _stream()), "moe_route")
+
+
+def moe_expert_tokens(h: torch.Tensor, gate_up: Optional[torch.Tensor], down: Optional[torch.Tensor], idx: torch.Tensor,
+                      out: torch.Tensor, E: int, F: int, limit: float) -> None:
+    """Expert outputs per (token, choice), unweighted: out [ntok, top, W]; choices >= E copy h (identity experts)."""
+    _chk(h, "h", _SEQ_ACT); _chk(out, "out", (h.dtype,)); _chk(idx, "idx", (torch.int32,))
+    _chk(gate_up, "gate_up", (h.dtype,), allow_none=E == 0); _chk(down, "down", (h.dtype,), allow_none=E == 0)
+    ntok, W = h.shape
+    top = idx.shape[1]
+    if out.shape != (ntok, top, W) or (E and (gate_up.shape != (E, 2 * F, W) or down.shape != (E, W, F))):
+        raise ValueError("moe_expert_tokens: shapes do not match")
+    _seq(_lib.load_seq().qspec_moe_expert_tokens(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top,
+                                                 float(limit), _sdt(h), _stream()), "moe_expert_tokens")

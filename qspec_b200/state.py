@@ -1,0 +1,119 @@
+"""Sequence-state manager shared by the models that the scheduler serves: slots, positions, and the per-step token
+table the kernels read.
+
+A live request owns one slot. What a slot holds is the model's business (key/value rows, convolution tails, ...); this
+module owns the bookkeeping that is the same for every model: which slots are free, how many tokens each sequence has
+consumed, and the flat description of a step (`BatchMeta`) -- for every token its slot, its position, where its
+sequence's tokens begin and end in the batch, and which of the two tail buffers holds the state from before the step.
+State that a slot held is never cleared on release: the kernels decide from positions alone what is valid, so a reused
+slot cannot leak rows of its previous owner.
+
+The reference leaves all of this to vLLM's block manager and scheduler (vllm/core/scheduler.py, block_manager.py), which
+are outside the int4 path this framework rebuilds; this is the minimal equivalent the decode loop needs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Sequence, Tuple
+
+import torch
+
+META_ROWS = 5          # slot, pos, seg_begin, seg_end, phase (include/qspec_b200_seq.h)
+
+
+class SlotPool:
+    """Free list of state slots. The most recently released slot is handed out first."""
+
+    def __init__(self, n_slots: int):
+        if n_slots < 1:
+            raise ValueError("SlotPool: at least one slot")
+        self.n_slots = n_slots
+        self._free = list(range(n_slots - 1, -1, -1))
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise RuntimeError(f"all {self.n_slots} sequence slots are in use")
+        return self._free.pop()
+
+    def release(self, slot: int) -> None:
+        if slot in self._free or not 0 <= slot < self.n_slots:
+            raise ValueError(f"slot {slot} is not in use")
+        self._free.append(slot)
+
+    @property
+    def free(self) -> int:
+        return len(self._free)
+
+
+@dataclass
+class BatchMeta:
+    """One step's token table. `table` is the device int32 [5, ntok] the kernels read; the rest is host bookkeeping."""
+    table: torch.Tensor
+    ntok: int
+    segments: List[Tuple[Hashable, int, int, int]]     # (request id, slot, first position, token count)
+
+    @property
+    def slot(self) -> torch.Tensor:
+        return self.table[0]
+
+    @property
+    def pos(self) -> torch.Tensor:
+        return self.table[1]
+
+
+class SequenceTable:
+    """Slots, positions and tail phases of the live sequences."""
+
+    def __init__(self, n_slots: int, device, max_step_tokens: int):
+        self.pool = SlotPool(n_slots)
+        self.device = torch.device(device)
+        self.slot_of: Dict[Hashable, int] = {}
+        self.pos = [0] * n_slots            # tokens consumed so far
+        self.phase = [0] * n_slots          # tail buffer that holds the current state
+        self.max_step_tokens = max_step_tokens
+        pin = self.device.type == "cuda"
+        self._host = torch.zeros(META_ROWS, max_step_tokens, dtype=torch.int32, pin_memory=pin)
+
+    def open(self, rid: Hashable) -> int:
+        if rid in self.slot_of:
+            raise ValueError(f"request {rid!r} is already live")
+        slot = self.pool.alloc()
+        self.slot_of[rid] = slot
+        self.pos[slot] = 0
+        return slot
+
+    def close(self, rid: Hashable) -> None:
+        self.pool.release(self.slot_of.pop(rid))
+
+    def held_tokens(self) -> int:
+        return sum(self.pos[s] for s in self.slot_of.values())
+
+    def plan(self, segments: Sequence[Tuple[Hashable, int]]) -> BatchMeta:
+        """segments: (request id, number of new tokens), each request at most once; unknown requests get a slot."""
+        ntok = sum(n for _, n in segments)
+        if ntok > self.max_step_tokens:
+            raise ValueError(f"a step of {ntok} tokens exceeds max_step_tokens = {self.max_step_tokens}")
+        h = self._host
+        at, segs = 0, []
+        for rid, n in segments:
+            if n < 1:
+                raise ValueError("a segment needs at least one token")
+            slot = self.slot_of[rid] if rid in self.slot_of else self.open(rid)
+            if any(s[1] == slot for s in segs):
+                raise ValueError(f"request {rid!r} appears twice in one step")
+            p0 = self.pos[slot]
+            h[0, at:at + n] = slot
+            h[1, at:at + n] = torch.arange(p0, p0 + n, dtype=torch.int32)
+            h[2, at:at + n] = at
+            h[3, at:at + n] = at + n
+            h[4, at:at + n] = self.phase[slot]
+            segs.append((rid, slot, p0, n))
+            at += n
+        table = h[:, :ntok].contiguous().to(self.device, non_blocking=False)
+        return BatchMeta(table=table, ntok=ntok, segments=segs)
+
+    def commit(self, meta: BatchMeta) -> None:
+        """The step described by `meta` has been queued: its tokens now count as consumed."""
+        for _, slot, _, n in meta.segments:
+            self.pos[slot] += n
+            self.phase[slot] ^= 1
