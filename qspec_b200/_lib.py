@@ -122,6 +122,13 @@ SEQ_SIGNATURES = {
     "qspec_moe_expert_tokens": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         c_float, c_int, c_void_p]),
     "qspec_seq_argmax_rows": (c_int, [c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_void_p]),
+    "qspec_seq_chunk_attention_mma_supported": (c_int, [c_int, c_int, c_int, c_int]),
+    "qspec_seq_chunk_attention_mma": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                              c_int, c_int, c_int, c_float, c_float, c_void_p]),
+    "qspec_moe_expert_grouped_supported": (c_int, [c_int, c_int]),
+    "qspec_moe_grouped_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "qspec_moe_expert_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                         c_float, c_void_p, c_size_t, c_void_p]),
 }
 
 _lib = None

@@ -1,0 +1,437 @@
+// Tensor-core forms of the sequence-mixer kernels for many tokens per step (bfloat16 only; include/qspec_b200_seq.h):
+// chunk-local sigmoid attention over 64-query tiles and the grouped expert feed-forward. Both use the warp-level
+// mma.sync.m16n8k16 path with float32 accumulators, like this library's other attention kernel for many sequences
+// (seq_attention_kernel): the tiles are short (a chunk of keys; an expert's share of the tokens), and the operands are
+// gathered by row, which is what rules out one large TMA-fed tile per CTA here.
+#include "common.cuh"
+#include "../../include/qspec_b200_seq.h"
+
+namespace qspec {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// (hi, lo) split of two float32 weights: hi = bf16(w), lo = bf16(w - hi); hi + lo carries 16 mantissa bits.
+__device__ __forceinline__ void split_bf2(float w0, float w1, uint32_t& hi, uint32_t& lo) {
+  const bf16 h0 = __float2bfloat16_rn(w0), h1 = __float2bfloat16_rn(w1);
+  __nv_bfloat162 hv;
+  hv.x = h0; hv.y = h1;
+  hi = *reinterpret_cast<uint32_t*>(&hv);
+  lo = pack_bf2(w0 - __bfloat162float(h0), w1 - __bfloat162float(h1));
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Attention. One CTA (4 warps) per (64 consecutive batch tokens, query head). Keys come from two places:
+//  * the step's own rows: batch indices [kmin, tile end), row i sees j in [lb_i, i] (lb_i = first batch row of its chunk
+//    inside its segment);
+//  * the cache, for rows whose chunk began before their segment: cache rows [0, nc_i) of the row's slot. Segments with
+//    such rows are visited one after the other (a prompt tile has one; the caller sends decode-shaped batches elsewhere).
+// Scores and weights are float32; the weights enter P.V as a two-term bfloat16 split.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int D, int DV>
+__global__ void __launch_bounds__(128)
+chunk_attn_mma_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ ck, const bf16* __restrict__ cv,
+                      const float* __restrict__ bias, bf16* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G,
+                      int size, float scale, float softcap) {
+  pdl_enter();
+  constexpr int QP = D + 8, VP = 64 + 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
+  bf16* sK = sQ + 64 * QP;
+  bf16* sVt = sK + 64 * QP;
+  int* s_lb = reinterpret_cast<int*>(sVt + DV * VP);
+  int* s_nc = s_lb + 64;
+  int* s_sb = s_nc + 64;
+  int* s_slot = s_sb + 64;
+  int* s_seg = s_slot + 64;               // rows that open a cache segment
+  __shared__ int s_kmin, s_nseg;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int r0 = blockIdx.x * 64, h = blockIdx.y, g = h / (H / G);
+  const int koff = H * D + g * D, voff = H * D + G * D + g * DV;
+  if (tid == 0) { s_kmin = 0x7fffffff; s_nseg = 0; }
+  __syncthreads();
+  if (tid < 64) {
+    const int i = r0 + tid;
+    int lb = 0x7fffffff, nc = 0, sb = -1, slot = 0;
+    if (i < ntok) {
+      slot = meta[i];
+      const int pos = meta[ntok + i];
+      sb = meta[2 * ntok + i];
+      const int pos_start = pos - (i - sb);
+      const int lo = (pos / size) * size;
+      lb = max(sb, i - (pos - lo));
+      nc = lo < pos_start ? pos_start - lo : 0;
+      atomicMin(&s_kmin, lb);
+    }
+    s_lb[tid] = lb; s_nc[tid] = nc; s_sb[tid] = sb; s_slot[tid] = slot;
+  }
+  // Q tile
+  for (int v = tid; v < 64 * (D / 8); v += 128) {
+    const int r = v / (D / 8), c = (v % (D / 8)) * 8;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (r0 + r < ntok) val = *reinterpret_cast<const uint4*>(qkv + (size_t)(r0 + r) * ld + (size_t)h * D + c);
+    *reinterpret_cast<uint4*>(sQ + r * QP + c) = val;
+  }
+  __syncthreads();
+  if (tid == 0) {                          // segments of this tile that reach into the cache, in batch order
+    int n = 0, last = -1;
+    for (int r = 0; r < 64; ++r)
+      if (s_nc[r] > 0 && s_sb[r] != last) { s_seg[n++] = r; last = s_sb[r]; }
+    s_nseg = n;
+  }
+  uint32_t qf[D / 16][4];
+  {
+    const int ra = warp * 16 + gid;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qf[ks][0] = *reinterpret_cast<const uint32_t*>(sQ + ra * QP + ks * 16 + tig * 2);
+      qf[ks][1] = *reinterpret_cast<const uint32_t*>(sQ + (ra + 8) * QP + ks * 16 + tig * 2);
+      qf[ks][2] = *reinterpret_cast<const uint32_t*>(sQ + ra * QP + ks * 16 + 8 + tig * 2);
+      qf[ks][3] = *reinterpret_cast<const uint32_t*>(sQ + (ra + 8) * QP + ks * 16 + 8 + tig * 2);
+    }
+  }
+  __syncthreads();
+  float oacc[DV / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) oacc[nt][0] = oacc[nt][1] = oacc[nt][2] = oacc[nt][3] = 0.f;
+  const float b = bias[h];
+  const int rowA = warp * 16 + gid, rowB = rowA + 8;
+  const int iA = r0 + rowA, iB = r0 + rowB;
+  const int lbA = s_lb[rowA], lbB = s_lb[rowB];
+  const int nseg = s_nseg, kmin = s_kmin;
+  const int kend = min(r0 + 64, ntok);
+
+  // source 0: the step's own rows; sources 1..nseg: cache rows of one segment each
+  for (int src = 0; src <= nseg; ++src) {
+    int kb0, kb1, seg_sb = -1, seg_slot = 0;
+    if (src == 0) { kb0 = kmin; kb1 = kend; }
+    else { const int r = s_seg[src - 1]; kb0 = 0; kb1 = s_nc[r]; seg_sb = s_sb[r]; seg_slot = s_slot[r]; }
+    for (int kb = kb0; kb < kb1; kb += 64) {
+      __syncthreads();                     // previous tile consumed
+      for (int v = tid; v < 64 * (D / 8); v += 128) {
+        const int r = v / (D / 8), c = (v % (D / 8)) * 8;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (kb + r < kb1)
+          val = src == 0 ? *reinterpret_cast<const uint4*>(qkv + (size_t)(kb + r) * ld + koff + c)
+                         : *reinterpret_cast<const uint4*>(ck + (((size_t)seg_slot * size + kb + r) * G + g) * D + c);
+        *reinterpret_cast<uint4*>(sK + r * QP + c) = val;
+      }
+      for (int v = tid; v < 64 * (DV / 8); v += 128) {
+        const int r = v % 64, c = (v / 64) * 8;   // consecutive threads take consecutive keys: conflict-free transposed stores
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (kb + r < kb1)
+          val = src == 0 ? *reinterpret_cast<const uint4*>(qkv + (size_t)(kb + r) * ld + voff + c)
+                         : *reinterpret_cast<const uint4*>(cv + (((size_t)seg_slot * size + kb + r) * G + g) * DV + c);
+        const bf16* e = reinterpret_cast<const bf16*>(&val);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) sVt[(c + x) * VP + r] = e[x];
+      }
+      __syncthreads();
+      float sacc[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const bf16* kp = sK + (nt * 8 + gid) * QP + ks * 16 + tig * 2;
+          mma_bf16_16816(sacc[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kp), *reinterpret_cast<const uint32_t*>(kp + 8));
+        }
+      }
+      // weights
+      bool okA, okB;
+      int hiA, hiB, loA, loB;                // visible key range of the two rows in this source's index space
+      if (src == 0) { loA = lbA; hiA = iA; loB = lbB; hiB = iB; okA = iA < ntok; okB = iB < ntok; }
+      else {
+        okA = s_sb[rowA] == seg_sb && s_nc[rowA] > 0; okB = s_sb[rowB] == seg_sb && s_nc[rowB] > 0;
+        loA = loB = 0; hiA = s_nc[rowA] - 1; hiB = s_nc[rowB] - 1;
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = kb + nt * 8 + tig * 2 + (e & 1);
+          const bool vis = e < 2 ? (okA && j >= loA && j <= hiA) : (okB && j >= loB && j <= hiB);
+          float s = sacc[nt][e] * scale;
+          if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+          sacc[nt][e] = vis ? 1.0f / (1.0f + expf(-(s + b))) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t ah[4], al[4];
+        split_bf2(sacc[2 * j][0], sacc[2 * j][1], ah[0], al[0]);
+        split_bf2(sacc[2 * j][2], sacc[2 * j][3], ah[1], al[1]);
+        split_bf2(sacc[2 * j + 1][0], sacc[2 * j + 1][1], ah[2], al[2]);
+        split_bf2(sacc[2 * j + 1][2], sacc[2 * j + 1][3], ah[3], al[3]);
+#pragma unroll
+        for (int nt = 0; nt < DV / 8; ++nt) {
+          const bf16* vp = sVt + (nt * 8 + gid) * VP + j * 16 + tig * 2;
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(vp), b1 = *reinterpret_cast<const uint32_t*>(vp + 8);
+          mma_bf16_16816(oacc[nt], ah, b0, b1);
+          mma_bf16_16816(oacc[nt], al, b0, b1);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < DV / 8; ++nt) {
+    const int c = h * DV + nt * 8 + tig * 2;
+    if (iA < ntok) *reinterpret_cast<uint32_t*>(out + (size_t)iA * H * DV + c) = pack_bf2(oacc[nt][0], oacc[nt][1]);
+    if (iB < ntok) *reinterpret_cast<uint32_t*>(out + (size_t)iB * H * DV + c) = pack_bf2(oacc[nt][2], oacc[nt][3]);
+  }
+}
+
+template <int D, int DV>
+static int launch_attn_mma(const void* qkv, int ld, const void* ck, const void* cv, const float* bias, void* out, const int* meta,
+                           int ntok, int H, int G, int size, float scale, float softcap, cudaStream_t st) {
+  constexpr size_t smem = (size_t)(2 * 64 * (D + 8) + DV * 72) * sizeof(bf16) + 5 * 64 * sizeof(int);
+  static bool configured = false;
+  if (!configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_mma_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  launch_pdl(chunk_attn_mma_kernel<D, DV>, dim3((ntok + 63) / 64, H), dim3(128), smem, st, (const bf16*)qkv, ld, (const bf16*)ck,
+             (const bf16*)cv, bias, (bf16*)out, meta, ntok, H, G, size, scale, softcap);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Grouped expert feed-forward. (1) moe_group_kernel sorts the (token, choice) pairs by expert and lists the 64-row tiles;
+// (2) grouped_gemm_kernel<true>: [gate ; up] products of the gathered token rows, clamped-gated activation, Y rows in
+// sorted order; (3) grouped_gemm_kernel<false>: down products, rows scattered back to out[token, choice]. Pairs whose
+// choice is an identity expert are copied by moe_identity_kernel.
+// ---------------------------------------------------------------------------------------------------------------------
+struct GroupPlan {
+  int* offsets;      // [E + 1] first sorted row of every expert
+  int* cursor;       // [E]
+  int* ntiles;       // [1]
+  int* tile_expert;  // [max tiles]
+  int* tile_row0;    // [max tiles]
+  int* perm;         // [npairs] sorted row -> pair index
+};
+
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ idx, int npairs, int E, GroupPlan p) {
+  pdl_enter();
+  extern __shared__ int s_cnt[];          // [E + 1]
+  const int tid = threadIdx.x;
+  for (int e = tid; e <= E; e += 1024) s_cnt[e] = 0;
+  __syncthreads();
+  for (int k = tid; k < npairs; k += 1024) {
+    const int e = idx[k];
+    if (e >= 0 && e < E) atomicAdd(&s_cnt[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = s_cnt[e];
+      p.offsets[e] = at;
+      for (int r = 0; r < c; r += 64) { p.tile_expert[nt] = e; p.tile_row0[nt] = at + r; ++nt; }
+      s_cnt[e] = at;                      // becomes the cursor
+      at += c;
+    }
+    p.offsets[E] = at;
+    *p.ntiles = nt;
+  }
+  __syncthreads();
+  for (int k = tid; k < npairs; k += 1024) {
+    const int e = idx[k];
+    if (e >= 0 && e < E) p.perm[atomicAdd(&s_cnt[e], 1)] = k;
+  }
+}
+
+__global__ void __launch_bounds__(128) moe_identity_kernel(const bf16* __restrict__ h, const int* __restrict__ idx, bf16* __restrict__ out,
+                                                           int W, int E, int top) {
+  pdl_enter();
+  const int k = blockIdx.x;
+  const int e = idx[k];
+  if (e >= 0 && e < E) return;
+  const bf16* src = h + (size_t)(k / top) * W;
+  bf16* dst = out + (size_t)k * W;
+  for (int c = threadIdx.x; c < W; c += 128) dst[c] = src[c];
+}
+
+// C[m, n] = sum_k A[row(m), k] * B_e[n, k] over the rows of one expert tile. 64 x 64 output tile, k-steps of 32, 4 warps
+// (16 rows each). DUAL: two B matrices (gate rows n and up rows F + n) and the activation epilogue.
+template <bool DUAL>
+__global__ void __launch_bounds__(128)
+grouped_gemm_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, GroupPlan p, int K, int N, int top,
+                    float limit) {
+  pdl_enter();
+  constexpr int KP = 32 + 8;
+  __shared__ __align__(16) bf16 sA[64 * KP];
+  __shared__ __align__(16) bf16 sB[(DUAL ? 2 : 1) * 64 * KP];
+  __shared__ int s_row[64];
+  const int tile = blockIdx.x;
+  if (tile >= *p.ntiles) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int e = p.tile_expert[tile], m0 = p.tile_row0[tile];
+  const int mend = p.offsets[e + 1];
+  const int n0 = blockIdx.y * 64;
+  if (tid < 64) {
+    const int m = m0 + tid;
+    s_row[tid] = m < mend ? p.perm[m] : -1;
+  }
+  __syncthreads();
+  const bf16* Be = B + (size_t)e * (DUAL ? 2 : 1) * N * K;
+  float acc[DUAL ? 2 : 1][8][4];
+#pragma unroll
+  for (int d = 0; d < (DUAL ? 2 : 1); ++d)
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) acc[d][nt][0] = acc[d][nt][1] = acc[d][nt][2] = acc[d][nt][3] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    __syncthreads();
+    for (int v = tid; v < 64 * 4; v += 128) {
+      const int r = v >> 2, c = (v & 3) * 8;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      const int pr = s_row[r];
+      if (pr >= 0 && k0 + c < K) {
+        const bf16* src = DUAL ? A + (size_t)(pr / top) * K : A + (size_t)(m0 + r) * K;
+        val = *reinterpret_cast<const uint4*>(src + k0 + c);
+      }
+      *reinterpret_cast<uint4*>(sA + r * KP + c) = val;
+    }
+    for (int v = tid; v < (DUAL ? 2 : 1) * 64 * 4; v += 128) {
+      const int d = v / 256, r = (v % 256) >> 2, c = (v & 3) * 8;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (n0 + r < N && k0 + c < K) val = *reinterpret_cast<const uint4*>(Be + ((size_t)d * N + n0 + r) * K + k0 + c);
+      *reinterpret_cast<uint4*>(sB + (d * 64 + r) * KP + c) = val;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t a[4];
+      const bf16* ap = sA + (warp * 16 + gid) * KP + ks * 16 + tig * 2;
+      a[0] = *reinterpret_cast<const uint32_t*>(ap);
+      a[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * KP);
+      a[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * KP + 8);
+#pragma unroll
+      for (int d = 0; d < (DUAL ? 2 : 1); ++d)
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          const bf16* bp = sB + (d * 64 + nt * 8 + gid) * KP + ks * 16 + tig * 2;
+          mma_bf16_16816(acc[d][nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
+        }
+    }
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = warp * 16 + gid + half * 8;
+    const int pr = s_row[r];
+    if (pr < 0) continue;
+    bf16* crow = DUAL ? C + (size_t)(m0 + r) * N : C + (size_t)pr * N;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int n = n0 + nt * 8 + tig * 2;
+      float v0, v1;
+      if (DUAL) {
+        // projections leave the matrix unit in bfloat16, like the dense layers' products
+        float gq0 = fminf(__bfloat162float(__float2bfloat16_rn(acc[0][nt][half * 2])), limit);
+        float gq1 = fminf(__bfloat162float(__float2bfloat16_rn(acc[0][nt][half * 2 + 1])), limit);
+        float uq0 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(acc[DUAL ? 1 : 0][nt][half * 2])), -limit), limit);
+        float uq1 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(acc[DUAL ? 1 : 0][nt][half * 2 + 1])), -limit), limit);
+        v0 = gq0 * (1.0f / (1.0f + expf(-1.702f * gq0))) * (uq0 + 1.0f);
+        v1 = gq1 * (1.0f / (1.0f + expf(-1.702f * gq1))) * (uq1 + 1.0f);
+      } else {
+        v0 = acc[0][nt][half * 2];
+        v1 = acc[0][nt][half * 2 + 1];
+      }
+      if (n + 1 < N) *reinterpret_cast<uint32_t*>(crow + n) = pack_bf2(v0, v1);
+      else if (n < N) crow[n] = __float2bfloat16_rn(v0);
+    }
+  }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace qspec
+
+using namespace qspec;
+
+extern "C" int qspec_seq_chunk_attention_mma_supported(int H, int G, int D, int DV) {
+  return H > 0 && G > 0 && H % G == 0 && (D == 64 || D == 128) && (DV == 64 || DV == 128);
+}
+
+extern "C" int qspec_seq_chunk_attention_mma(const void* qkv, int ld, const void* cache_k, const void* cache_v, const float* bias,
+                                             void* out, const int* meta, int ntok, int H, int G, int D, int DV, int size,
+                                             float scale, float softcap, void* stream) {
+  QSPEC_REQUIRE(qkv && cache_k && cache_v && bias && out && meta, QSPEC_ERR_INVALID_ARG, "seq_chunk_attention_mma: null pointer");
+  QSPEC_REQUIRE(qspec_seq_chunk_attention_mma_supported(H, G, D, DV), QSPEC_ERR_UNSUPPORTED,
+                "seq_chunk_attention_mma: head sizes %d / %d (64 or 128 each)", D, DV);
+  QSPEC_REQUIRE(ntok >= 0 && size > 0 && ld >= H * D + G * (D + DV) && ld % 8 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+                    ((uintptr_t)cache_k & 15) == 0 && ((uintptr_t)cache_v & 15) == 0,
+                QSPEC_ERR_UNSUPPORTED, "seq_chunk_attention_mma: rows must be 16-byte aligned (ld %d)", ld);
+  if (ntok == 0) return QSPEC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 64 && DV == 64) return launch_attn_mma<64, 64>(qkv, ld, cache_k, cache_v, bias, out, meta, ntok, H, G, size, scale, softcap, st);
+  if (D == 64 && DV == 128) return launch_attn_mma<64, 128>(qkv, ld, cache_k, cache_v, bias, out, meta, ntok, H, G, size, scale, softcap, st);
+  if (D == 128 && DV == 64) return launch_attn_mma<128, 64>(qkv, ld, cache_k, cache_v, bias, out, meta, ntok, H, G, size, scale, softcap, st);
+  return launch_attn_mma<128, 128>(qkv, ld, cache_k, cache_v, bias, out, meta, ntok, H, G, size, scale, softcap, st);
+}
+
+extern "C" int qspec_moe_expert_grouped_supported(int W, int F) { return W > 0 && F > 0 && W % 8 == 0 && F % 8 == 0; }
+
+static size_t grouped_layout(int ntok, int top, int E, int F, size_t* off) {
+  const size_t npairs = (size_t)ntok * top, max_tiles = npairs / 64 + E + 1;
+  size_t at = 0;
+  off[0] = at; at = align_up(at + (size_t)(E + 1) * 4, 16);      // offsets
+  off[1] = at; at = align_up(at + (size_t)(E + 1) * 4, 16);      // cursor (unused slot kept for alignment of the plan)
+  off[2] = at; at = align_up(at + 4, 16);                        // ntiles
+  off[3] = at; at = align_up(at + max_tiles * 4, 16);            // tile_expert
+  off[4] = at; at = align_up(at + max_tiles * 4, 16);            // tile_row0
+  off[5] = at; at = align_up(at + npairs * 4, 16);               // perm
+  off[6] = at; at = align_up(at + npairs * (size_t)F * 2, 16);   // Y
+  return at;
+}
+
+extern "C" size_t qspec_moe_grouped_workspace_bytes(int ntok, int top, int E, int F) {
+  size_t off[7];
+  return grouped_layout(ntok > 0 ? ntok : 0, top, E, F, off);
+}
+
+extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
+                                        int W, int F, int E, int top, float limit, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  QSPEC_REQUIRE(h && idx && out && workspace && (E == 0 || (gate_up && down)), QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && top >= 1 && E >= 0 && E <= 8192, QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: bad sizes");
+  QSPEC_REQUIRE(qspec_moe_expert_grouped_supported(W, F), QSPEC_ERR_UNSUPPORTED,
+                "moe_expert_grouped: width %d and expert size %d must be multiples of 8", W, F);
+  QSPEC_REQUIRE((((uintptr_t)h | (uintptr_t)gate_up | (uintptr_t)down | (uintptr_t)out | (uintptr_t)workspace) & 15) == 0,
+                QSPEC_ERR_UNSUPPORTED, "moe_expert_grouped: pointers must be 16-byte aligned");
+  size_t off[7];
+  QSPEC_REQUIRE(workspace_bytes >= grouped_layout(ntok, top, E, F, off), QSPEC_ERR_WORKSPACE, "moe_expert_grouped: workspace too small");
+  if (ntok == 0) return QSPEC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned char* ws = (unsigned char*)workspace;
+  GroupPlan p;
+  p.offsets = (int*)(ws + off[0]); p.cursor = (int*)(ws + off[1]); p.ntiles = (int*)(ws + off[2]);
+  p.tile_expert = (int*)(ws + off[3]); p.tile_row0 = (int*)(ws + off[4]); p.perm = (int*)(ws + off[5]);
+  bf16* Y = (bf16*)(ws + off[6]);
+  const int npairs = ntok * top;
+  const int max_tiles = npairs / 64 + E + 1;
+  launch_pdl(moe_identity_kernel, dim3(npairs), dim3(128), 0, st, (const bf16*)h, idx, (bf16*)out, W, E, top);
+  QSPEC_CHECK_LAUNCH(1);
+  if (E == 0) return QSPEC_OK;
+  launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), st, idx, npairs, E, p);
+  QSPEC_CHECK_LAUNCH(1);
+  launch_pdl(grouped_gemm_kernel<true>, dim3(max_tiles, (F + 63) / 64), dim3(128), 0, st, (const bf16*)h, (const bf16*)gate_up, Y, p, W,
+             F, top, limit);
+  QSPEC_CHECK_LAUNCH(1);
+  launch_pdl(grouped_gemm_kernel<false>, dim3(max_tiles, (W + 63) / 64), dim3(128), 0, st, (const bf16*)Y, (const bf16*)down, (bf16*)out,
+             p, F, W, top, limit);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}

@@ -254,6 +254,9 @@ class MutusunModel(torch.nn.Module):
         self.buf_rw = torch.empty(T * tops, **f32)
         self.buf_pair = torch.empty(T * tops * W if has_moe else 1, **act)
         self.buf_ids = torch.empty(T, dtype=torch.int32, device=dev)
+        # Prompt-shaped batches take the tensor-core tile kernels (bfloat16); QSPEC_SEQ_TILES=0 keeps the token-per-CTA forms.
+        self.use_tiles = dtype == torch.bfloat16 and os.environ.get("QSPEC_SEQ_TILES", "1") != "0"
+        self.tiles_min_tokens = 64           # a step with fewer tokens, or fewer than 16 per sequence, is decode-shaped
 
     # ------------------------------------------------------------------------------------------
     @classmethod
@@ -287,6 +290,7 @@ class MutusunModel(torch.nn.Module):
         h = self.buf_h[:T * W].view(T, W)
         ya, yb = self.buf_y[0][:T * W].view(T, W), self.buf_y[1][:T * W].view(T, W)
         ops.seq_embed(self.embed, input_ids, xa)
+        prompt_shaped = self.use_tiles and T >= self.tiles_min_tokens and T >= 16 * len(meta.segments)
         pend = None                                    # (y, part weights, post-norm weight) of the sublayer still to be added
 
         def enter(pre_w, conv_w, tail, out):
@@ -307,7 +311,8 @@ class MutusunModel(torch.nn.Module):
             torch.matmul(h, p.qkv.t(), out=qkv)
             ops.seq_qk_norm(qkv, p.q_norm, p.k_norm, m.heads, m.kv_heads, m.dim, eps)
             ops.seq_chunk_attention(qkv, self.cache_k[i], self.cache_v[i], p.pb, att, tab, m.heads, m.kv_heads, m.dim, m.vdim,
-                                    m.chunk, m.scale, m.softcap)
+                                    m.chunk, m.scale, m.softcap,
+                                    tiles=prompt_shaped and ops.seq_chunk_attention_tiles_supported(qkv, m.heads, m.kv_heads, m.dim, m.vdim))
             ops.seq_cache_append(qkv, self.cache_k[i], self.cache_v[i], tab, m.heads, m.kv_heads, m.dim, m.vdim, m.chunk)
             torch.matmul(att, p.o.t(), out=ya)
             pend = (ya, None, p.norm1b)
@@ -324,7 +329,10 @@ class MutusunModel(torch.nn.Module):
                     rw = self.buf_rw[:T * f.top].view(T, f.top)
                     pair = self.buf_pair[:T * f.top * W].view(T, f.top, W)
                     ops.moe_route(h, p.router, p.correction, idx, rw)
-                    ops.moe_expert_tokens(h, p.gate_up, p.edown, idx, pair, f.experts, f.ff, f.limit)
+                    if self.use_tiles and T >= self.tiles_min_tokens and ops.moe_expert_grouped_supported(h, f.ff):
+                        ops.moe_expert_grouped(h, p.gate_up, p.edown, idx, pair, f.experts, f.ff, f.limit)
+                    else:
+                        ops.moe_expert_tokens(h, p.gate_up, p.edown, idx, pair, f.experts, f.ff, f.limit)
                     pend = (pair, rw, p.norm2b)
             if trace is not None:
                 enter(None, None, None, None)          # residual sum only

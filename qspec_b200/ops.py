@@ -807,15 +807,28 @@ def seq_qk_norm(qkv: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, H: int,
                                            _sdt(qkv), _stream()), "seq_qk_norm")
 
 
+def seq_chunk_attention_tiles_supported(qkv: torch.Tensor, H: int, G: int, D: int, DV: int) -> bool:
+    """The tensor-core tile form takes bfloat16 rows that start on 16-byte boundaries and head sizes of 64 or 128."""
+    return bool(qkv.dtype == _BF16 and qkv.shape[1] % 8 == 0
+                and _lib.load_seq().qspec_seq_chunk_attention_mma_supported(H, G, D, DV))
+
+
 def seq_chunk_attention(qkv: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, bias: torch.Tensor, out: torch.Tensor,
-                        meta: torch.Tensor, H: int, G: int, D: int, DV: int, size: int, scale: float, softcap: float) -> None:
-    """Chunk-local sigmoid attention of a token batch; cache_k [slots, size, G, D], cache_v [slots, size, G, DV]."""
+                        meta: torch.Tensor, H: int, G: int, D: int, DV: int, size: int, scale: float, softcap: float,
+                        tiles: bool = False) -> None:
+    """Chunk-local sigmoid attention of a token batch; cache_k [slots, size, G, D], cache_v [slots, size, G, DV].
+    tiles=True: the tensor-core form over 64-query tiles (prompt-shaped batches; `seq_chunk_attention_tiles_supported`)."""
     for t, n in ((qkv, "qkv"), (cache_k, "cache_k"), (cache_v, "cache_v"), (out, "out")):
         _chk(t, n, (qkv.dtype,))
     _chk(qkv, "qkv", _SEQ_ACT); _chk(bias, "bias", (_F32,)); _chk(meta, "meta", (torch.int32,))
     ntok = qkv.shape[0]
     if out.shape != (ntok, H * DV) or meta.shape != (5, ntok) or cache_k.shape[1:] != (size, G, D) or cache_v.shape[1:] != (size, G, DV):
         raise ValueError("seq_chunk_attention: shapes do not match")
+    if tiles:
+        _seq(_lib.load_seq().qspec_seq_chunk_attention_mma(_ptr(qkv), qkv.shape[1], _ptr(cache_k), _ptr(cache_v), _ptr(bias), _ptr(out),
+                                                           _ptr(meta), ntok, H, G, D, DV, size, float(scale), float(softcap or 0.0),
+                                                           _stream()), "seq_chunk_attention (tiles)")
+        return
     _seq(_lib.load_seq().qspec_seq_chunk_attention(_ptr(qkv), qkv.shape[1], _ptr(cache_k), _ptr(cache_v), _ptr(bias), _ptr(out),
                                                    _ptr(meta), ntok, H, G, D, DV, size, float(scale), float(softcap or 0.0),
                                                    _sdt(qkv), _stream()), "seq_chunk_attention")
@@ -858,3 +871,23 @@ def moe_expert_tokens(h: torch.Tensor, gate_up: Optional[torch.Tensor], down: Op
         raise ValueError("moe_expert_tokens: shapes do not match")
     _seq(_lib.load_seq().qspec_moe_expert_tokens(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top,
                                                  float(limit), _sdt(h), _stream()), "moe_expert_tokens")
+
+
+def moe_expert_grouped_supported(h: torch.Tensor, F: int) -> bool:
+    return bool(h.dtype == _BF16 and _lib.load_seq().qspec_moe_expert_grouped_supported(h.shape[1], F))
+
+
+def moe_expert_grouped(h: torch.Tensor, gate_up: Optional[torch.Tensor], down: Optional[torch.Tensor], idx: torch.Tensor,
+                       out: torch.Tensor, E: int, F: int, limit: float) -> None:
+    """`moe_expert_tokens` for many tokens (bfloat16): the (token, choice) pairs are sorted by expert and every expert's rows
+    go through tensor-core tiles; same outputs up to the summation order."""
+    _chk(h, "h", (_BF16,)); _chk(out, "out", (_BF16,)); _chk(idx, "idx", (torch.int32,))
+    _chk(gate_up, "gate_up", (_BF16,), allow_none=E == 0); _chk(down, "down", (_BF16,), allow_none=E == 0)
+    ntok, W = h.shape
+    top = idx.shape[1]
+    if out.shape != (ntok, top, W) or (E and (gate_up.shape != (E, 2 * F, W) or down.shape != (E, W, F))):
+        raise ValueError("moe_expert_grouped: shapes do not match")
+    lib = _lib.load_seq()
+    ws = _workspace("moe_grouped", lib.qspec_moe_grouped_workspace_bytes(ntok, top, E, F), h.device)
+    _seq(lib.qspec_moe_expert_grouped(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top, float(limit),
+                                      _ptr(ws), ws.numel(), _stream()), "moe_expert_grouped")

@@ -45,8 +45,6 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.finished: Dict[Hashable, Request] = {}
-        pin = torch.device(model.device).type == "cuda"
-        self._ids_host = torch.zeros(model.max_step_tokens, dtype=torch.int32, pin_memory=pin)
         self.steps = 0
 
     # ---- the step function ----------------------------------------------------------------------------------------
@@ -77,14 +75,14 @@ class Scheduler:
             base += len(want)
         work = [(e, 0) for e in range(len(entries)) if len(entries[e][1])]
         while work:
-            segs, rows, at, nxt = [], [], 0, []
+            segs, rows, at, nxt, ids = [], [], 0, [], []
             for e, done in work:
                 rid, toks, want = entries[e]
                 n = min(len(toks) - done, cap - at)
                 if n <= 0:
                     nxt.append((e, done))
                     continue
-                self._ids_host[at:at + n] = torch.as_tensor(list(toks[done:done + n]), dtype=torch.int32)
+                ids.extend(toks[done:done + n])
                 segs.append((rid, n))
                 for k, w in enumerate(want):
                     if done <= w < done + n:
@@ -92,9 +90,8 @@ class Scheduler:
                 at += n
                 if done + n < len(toks):
                     nxt.append((e, done + n))
-            meta = self.table.plan(segs)
-            ids = self._ids_host[:at].to(model.device, non_blocking=True)
-            hidden = model.forward_batch(ids, meta)
+            meta = self.table.plan(segs, ids)
+            hidden = model.forward_batch(meta.ids, meta)
             self.table.commit(meta)
             if rows:
                 sel = torch.tensor([r for _, r in rows], dtype=torch.int64, device=model.device)

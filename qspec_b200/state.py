@@ -49,6 +49,7 @@ class SlotPool:
 class BatchMeta:
     """One step's token table. `table` is the device int32 [5, ntok] the kernels read; the rest is host bookkeeping."""
     table: torch.Tensor
+    ids: torch.Tensor                                  # device int32 [ntok]: the step's token ids (zeros if none were given)
     ntok: int
     segments: List[Tuple[Hashable, int, int, int]]     # (request id, slot, first position, token count)
 
@@ -71,8 +72,6 @@ class SequenceTable:
         self.pos = [0] * n_slots            # tokens consumed so far
         self.phase = [0] * n_slots          # tail buffer that holds the current state
         self.max_step_tokens = max_step_tokens
-        pin = self.device.type == "cuda"
-        self._host = torch.zeros(META_ROWS, max_step_tokens, dtype=torch.int32, pin_memory=pin)
 
     def open(self, rid: Hashable) -> int:
         if rid in self.slot_of:
@@ -88,12 +87,19 @@ class SequenceTable:
     def held_tokens(self) -> int:
         return sum(self.pos[s] for s in self.slot_of.values())
 
-    def plan(self, segments: Sequence[Tuple[Hashable, int]]) -> BatchMeta:
-        """segments: (request id, number of new tokens), each request at most once; unknown requests get a slot."""
+    def plan(self, segments: Sequence[Tuple[Hashable, int]], token_ids: Sequence[int] = None) -> BatchMeta:
+        """segments: (request id, number of new tokens), each request at most once; unknown requests get a slot.
+        token_ids: the step's tokens in batch order; they travel to the device in the same copy as the table.
+        Every step stages its table in a fresh pinned block: the copy is asynchronous, and the host may plan the next
+        step before the device has fetched this one."""
         ntok = sum(n for _, n in segments)
         if ntok > self.max_step_tokens:
             raise ValueError(f"a step of {ntok} tokens exceeds max_step_tokens = {self.max_step_tokens}")
-        h = self._host
+        if token_ids is not None and len(token_ids) != ntok:
+            raise ValueError(f"{len(token_ids)} token ids for a step of {ntok} tokens")
+        h = torch.zeros(META_ROWS + 1, ntok, dtype=torch.int32)
+        if token_ids is not None:
+            h[META_ROWS] = torch.as_tensor(token_ids, dtype=torch.int32)
         at, segs = 0, []
         for rid, n in segments:
             if n < 1:
@@ -109,8 +115,10 @@ class SequenceTable:
             h[4, at:at + n] = self.phase[slot]
             segs.append((rid, slot, p0, n))
             at += n
-        table = h[:, :ntok].contiguous().to(self.device, non_blocking=False)
-        return BatchMeta(table=table, ntok=ntok, segments=segs)
+        if self.device.type == "cuda":
+            h = h.pin_memory()
+        dev = h.to(self.device, non_blocking=True)
+        return BatchMeta(table=dev[:META_ROWS], ids=dev[META_ROWS], ntok=ntok, segments=segs)
 
     def commit(self, meta: BatchMeta) -> None:
         """The step described by `meta` has been queued: its tokens now count as consumed."""
