@@ -1,0 +1,287 @@
+"""`bench.py --design mutusun`: prefill and decode throughput of the Mutusun design at sizes that resemble a real model's
+layers (random weights), next to the framework's int4 Llama decoder at equal width / heads / feed-forward size, both
+through the same scheduler; plus the design's kernels one by one against their roofline and against the like kernel of
+the int4 decoder. Prints one JSON line. The default workload of bench.py is untouched by this option.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+SIZES = {
+    # width, heads, kv, dim, chunk, dense ff, (experts, expert ff, identity, top)
+    "w2048": dict(width=2048, heads=16, kv=4, dim=128, chunk=1024, ff=7168, moe=(16, 1024, 2, 4)),
+    "w4096": dict(width=4096, heads=32, kv=8, dim=128, chunk=2048, ff=14336, moe=(8, 2048, 1, 2)),
+}
+VOCAB = 32000
+
+
+def mutusun_config(s):
+    mixer = {"heads": s["heads"], "kv_heads": s["kv"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5, "softcap": 30.0,
+             "mask": {"size": s["chunk"]}}
+    E, F, ident, top = s["moe"]
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": F, "limit": 7.0}, "router": {"experts": E, "identity": ident, "top": top}}
+    layers = [{"type": "attention", "mixer": mixer, "mlp": dense}, {"type": "attention", "mixer": mixer, "mlp": moe},
+              {"type": "attention", "mixer": mixer, "mlp": dense, "weights_of": 0}, {"type": "attention", "mixer": mixer, "mlp": moe, "weights_of": 1}]
+    return {"architecture": "Mutusun", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": layers}
+
+
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _throughput(torch, sched, vocab, n_seqs, ctx, prompt, portion, steps, warmup):
+    """Prefill: one request of `prompt` tokens in portions. Decode: n_seqs requests with `ctx` tokens each, one token per
+    sequence per step through Scheduler.step (greedy sampling, tokens read back every step)."""
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, vocab, (prompt,), generator=g).tolist()
+    for rep in range(2):                                   # first pass warms up
+        torch.cuda.synchronize()
+        a, b = _events(torch)
+        a.record()
+        at = 0
+        while at < prompt:
+            n = min(portion, prompt - at)
+            sched.feed([("p", toks[at:at + n], [n - 1] if at + n == prompt else [])])
+            at += n
+        b.record(); b.synchronize()
+        sched.release("p")
+        prefill_ms = a.elapsed_time(b)
+    for k in range(n_seqs):
+        # long enough that no request finishes inside the timed steps: the batch stays at n_seqs tokens (a changing token
+        # count sends every dense product through the vendor library's heuristics again, which is not the steady state)
+        sched.add(("d", k), torch.randint(0, vocab, (ctx,), generator=g).tolist(), max_new_tokens=warmup + steps + 4 * n_seqs)
+    while any(r.fed < len(r.prompt) for r in list(sched.waiting) + sched.running):
+        sched.step()
+    for _ in range(warmup):
+        sched.step()
+    torch.cuda.synchronize()
+    a, b = _events(torch)
+    t0 = time.perf_counter()
+    a.record()
+    n = 0
+    for _ in range(steps):
+        n += len(sched.step())
+    b.record(); b.synchronize()
+    wall = time.perf_counter() - t0
+    for r in list(sched.running):                          # retire the requests without decoding them to the end
+        sched.running.remove(r)
+        sched.release(r.rid)
+    return {"prefill_tokens_per_s": prompt / (prefill_ms / 1e3), "prefill_ms": prefill_ms, "prefill_tokens": prompt, "portion": portion,
+            "decode_tokens_per_s": n / (a.elapsed_time(b) / 1e3), "decode_ms_per_step": a.elapsed_time(b) / steps,
+            "decode_e2e_tokens_per_s": n / wall, "decode_seqs": n_seqs, "context": ctx}
+
+
+def _time_us(torch, fns, reps=20):
+    """Mean microseconds per call over `fns` called round robin (callers pass variants on distinct buffers that together
+    exceed the L2 where the kernel is meant to stream from HBM)."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    a, b = _events(torch)
+    a.record()
+    for r in range(reps):
+        fns[r % len(fns)]()
+    b.record(); b.synchronize()
+    return a.elapsed_time(b) * 1e3 / reps
+
+
+def _kernel_table(torch, s, hbm_gbs, bf16_tflops):
+    """Each Mutusun kernel at a prompt shape (T = 2048, one sequence) and a decode shape (64 sequences x 1 token), with the
+    like kernel of the int4 decoder at its own operating shapes. frac = achieved / measured peak of the binding resource."""
+    from . import ops
+    dev = "cuda"
+    W, H, G, D, size = s["width"], s["heads"], s["kv"], s["dim"], s["chunk"]
+    E, F, ident, top = s["moe"]
+    ld = H * D + 2 * G * D
+    bf, f32 = torch.bfloat16, torch.float32
+    rows = []
+
+    def meta(segs):
+        r = [[], [], [], [], []]
+        at = 0
+        for slot, p0, n in segs:
+            r[0] += [slot] * n; r[1] += list(range(p0, p0 + n)); r[2] += [at] * n; r[3] += [at + n] * n; r[4] += [0] * n
+            at += n
+        return torch.tensor(r, dtype=torch.int32, device=dev)
+
+    def add(name, shape, us, nbytes=None, flops=None, like=None):
+        e = {"kernel": name, "shape": shape, "us": round(us, 2)}
+        if nbytes is not None:
+            e["GBps"] = round(nbytes / us / 1e3, 1); e["frac_hbm"] = round(nbytes / us / 1e3 / hbm_gbs, 3)
+        if flops is not None:
+            e["TFLOPs"] = round(flops / us / 1e6, 1); e["frac_bf16"] = round(flops / us / 1e6 / bf16_tflops, 3)
+        if like:
+            e["like"] = like
+        rows.append(e)
+
+    shapes = {"prompt": [(0, 0, 2048)], "decode": [(k, size // 2 + k, 1) for k in range(64)]}
+    nslots = 64
+    copies = 3
+    ck = [torch.randn(nslots, size, G, D, device=dev).to(bf) for _ in range(copies)]
+    cv = [torch.randn(nslots, size, G, D, device=dev).to(bf) for _ in range(copies)]
+    pb = torch.zeros(H, device=dev)
+    for label, segs in shapes.items():
+        T = sum(n for _, _, n in segs)
+        tab = meta(segs)
+        nbuf = max(2, min(8, int(200e6 / (T * W * 12)) + 1))
+        x = [torch.randn(T, W, device=dev) for _ in range(nbuf)]
+        xo = [torch.empty(T, W, device=dev) for _ in range(nbuf)]
+        y = [torch.randn(T, W, device=dev).to(bf) for _ in range(nbuf)]
+        h = [torch.empty(T, W, device=dev, dtype=bf) for _ in range(nbuf)]
+        w1, w2 = torch.zeros(W, device=dev), torch.zeros(W, device=dev)
+        cw = torch.randn(W, 4, device=dev) * 0.1
+        tail = torch.zeros(2, nslots, 3, W, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.seq_norm_conv(x[i], tab, 1e-5, out=h[i], pre_w=w1, conv_w=cw, tail=tail, y=y[i], post_w=w2,
+                                                            x_out=xo[i]) for i in range(nbuf)])
+        add("seq_norm_conv (residual + 2 norms + conv)", f"{label} T={T} W={W}", us, nbytes=T * W * 12)
+        qkv = [(torch.randn(T, ld, device=dev) * 0.3).to(bf) for _ in range(nbuf)]
+        qn = torch.ones(D, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.seq_qk_norm(qkv[i], qn, qn, H, G, D, 1e-5) for i in range(nbuf)])
+        add("seq_qk_norm", f"{label} T={T}", us, nbytes=T * (H + G) * D * 4)
+        us = _time_us(torch, [lambda i=i: ops.seq_cache_append(qkv[i], ck[i % copies], cv[i % copies], tab, H, G, D, D, size) for i in range(nbuf)])
+        add("seq_cache_append", f"{label} T={T}", us, nbytes=T * 2 * G * D * 4)
+        att = torch.empty(T, H * D, device=dev, dtype=bf)
+        if label == "prompt":
+            us = _time_us(torch, [lambda i=i: ops.seq_chunk_attention(qkv[i], ck[0], cv[0], pb, att, tab, H, G, D, D, size, D ** -0.5, 30.0,
+                                                                      tiles=True) for i in range(nbuf)])
+            visible = sum((p % size) + 1 for p in range(T))
+            add("seq_chunk_attention (tiles)", f"T={T} chunk={size} H={H} G={G} D={D}", us, flops=2.0 * visible * H * 2 * D)
+            rows[-1]["note"] = ("algorithmic flops of the visible (query, key) pairs; the kernel issues the P.V product twice "
+                                "(two-term bfloat16 split of the float32 weights) and computes whole 64x64 tiles on the diagonal")
+        else:
+            us = _time_us(torch, [lambda i=i: ops.seq_chunk_attention(qkv[i % nbuf], ck[i % copies], cv[i % copies], pb, att, tab, H, G, D, D,
+                                                                      size, D ** -0.5, 30.0) for i in range(copies)])
+            visible = sum((p % size) + 1 for _, p, _ in segs)
+            add("seq_chunk_attention (token form)", f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * G * 2 * D * 2)
+        hb = [torch.randn(T, W, device=dev).to(bf) for _ in range(nbuf)]
+        rw = torch.randn(E + ident, W, device=dev) * 0.05
+        corr = torch.zeros(E + ident, device=dev)
+        idx = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wt = torch.empty(T, top, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.moe_route(hb[i], rw, corr, idx, wt) for i in range(nbuf)])
+        add("moe_route", f"{label} T={T} R={E + ident}", us, nbytes=T * W * 2)
+        gu = [(torch.randn(E, 2 * F, W, device=dev) * W ** -0.5).to(bf) for _ in range(2)]
+        dn = [(torch.randn(E, W, F, device=dev) * F ** -0.5).to(bf) for _ in range(2)]
+        pair = torch.empty(T, top, W, device=dev, dtype=bf)
+        real = int((idx < E).sum())
+        if label == "prompt":
+            us = _time_us(torch, [lambda i=i: ops.moe_expert_grouped(hb[i % nbuf], gu[i % 2], dn[i % 2], idx, pair, E, F, 7.0) for i in range(2)])
+            add("moe_expert_grouped (sort + 2 tile GEMMs)", f"T={T} top={top} E={E} F={F}", us, flops=2.0 * real * 3 * W * F)
+        else:
+            us = _time_us(torch, [lambda i=i: ops.moe_expert_tokens(hb[i % nbuf], gu[i % 2], dn[i % 2], idx, pair, E, F, 7.0) for i in range(2)])
+            touched = len(set(idx[idx < E].tolist()))
+            add("moe_expert_tokens", f"T={T} top={top}, {touched} of {E} experts touched", us, nbytes=touched * 3 * W * F * 2)
+            rows[-1]["note"] = ("bytes = the touched experts' weights once (each (token, choice) CTA re-reads its expert from L2); "
+                                "the model takes this form only below 4 rows per expert")
+            us = _time_us(torch, [lambda i=i: ops.moe_expert_grouped(hb[i % nbuf], gu[i % 2], dn[i % 2], idx, pair, E, F, 7.0) for i in range(2)])
+            add("moe_expert_grouped (sort + 2 tile GEMMs)", f"T={T} top={top}, {touched} of {E} experts touched", us,
+                nbytes=touched * 3 * W * F * 2)
+        # vendor products, for scale
+        wq = (torch.randn(ld, W, device=dev) * 0.02).to(bf)
+        o = torch.empty(T, ld, device=dev, dtype=bf)
+        us = _time_us(torch, [lambda i=i: torch.matmul(hb[i], wq.t(), out=o) for i in range(nbuf)])
+        add("qkv product (vendor library)", f"{label} {T}x{ld}x{W}", us, nbytes=(ld * W + T * W + T * ld) * 2, flops=2.0 * T * ld * W)
+        del x, xo, y, h, qkv, hb, gu, dn, pair
+    return rows
+
+
+def _like_kernels(torch, s, hbm_gbs, bf16_tflops):
+    """The int4 decoder's kernels of the same roles at its operating shapes (verify pass: 64 sequences x 4 tokens)."""
+    from . import ops
+    from .model import random_int4_linear
+    dev, f16 = "cuda", torch.float16
+    W, H, G, D = s["width"], s["heads"], s["kv"], s["dim"]
+    rows = []
+
+    def add(name, shape, us, nbytes=None, flops=None):
+        e = {"kernel": name, "shape": shape, "us": round(us, 2)}
+        if nbytes is not None:
+            e["GBps"] = round(nbytes / us / 1e3, 1); e["frac_hbm"] = round(nbytes / us / 1e3 / hbm_gbs, 3)
+        if flops is not None:
+            e["TFLOPs"] = round(flops / us / 1e6, 1); e["frac_bf16"] = round(flops / us / 1e6 / bf16_tflops, 3)
+        rows.append(e)
+
+    for T in (256, 64):
+        nbuf = 8
+        x = [torch.randn(T, W, device=dev).to(f16) for _ in range(nbuf)]
+        dl = [torch.randn(T, W, device=dev).to(f16) for _ in range(nbuf)]
+        out = torch.empty(T, W, device=dev, dtype=f16)
+        us = _time_us(torch, [lambda i=i: ops.add_rms_norm_fuse_sum_fp16(out, x[i], dl[i], 1e-5) for i in range(nbuf)])
+        add("add + norm (f16)", f"T={T} W={W}", us, nbytes=T * W * 8)
+    S, B = 1024, 64
+    ck = torch.randn(B, S, G, D, device=dev).to(f16)
+    cv = torch.randn(B, S, G, D, device=dev).to(f16)
+    for per in (4, 1):
+        T = B * per
+        qkv = (torch.randn(T, (H + 2 * G) * D, device=dev) * 0.3).to(f16)
+        pos = (torch.arange(T, device=dev, dtype=torch.int32) % per) + 512
+        sid = (torch.arange(T, device=dev, dtype=torch.int32) // per).contiguous()
+        att = torch.empty(T, H * D, device=dev, dtype=f16)
+        cs = torch.randn(S, D, device=dev).to(f16)
+        us = _time_us(torch, [lambda: ops.rope_kvcache(qkv, cs, pos, sid, ck, cv, H, G, D)])
+        add("rope + cache append", f"T={T}", us, nbytes=T * ((H + G) * D * 4 + 2 * G * D * 2))
+        if ops.seq_attention_supported(T, H, G, D, S):
+            us = _time_us(torch, [lambda: ops.seq_attention(qkv, ck, cv, pos, sid, att, H, G, D, D ** -0.5)])
+            add("seq_attention", f"64 seqs x {per}, 512 keys", us, nbytes=B * 513 * G * 2 * D * 2)
+        us = _time_us(torch, [lambda: ops.decode_attention(qkv, ck, cv, pos, sid, att, H, G, D, D ** -0.5)])
+        add("decode_attention", f"64 seqs x {per}, 512 keys", us, nbytes=B * 513 * G * 2 * D * 2)
+    ops.reserve_workspaces(256, [(s["ff"] * 2, W)], torch.device(dev))
+    lins = [random_int4_linear(2 * s["ff"], W, 100 + i, dev) for i in range(3)]
+    for T in (256, 64):
+        xin = torch.randn(T, W, device=dev).to(f16)
+        o = torch.empty(T, 2 * s["ff"], device=dev, dtype=f16)
+        us = _time_us(torch, [lambda l=l: l(xin, o) for l in lins])
+        add("W4A16 gate_up product", f"{T}x{2 * s['ff']}x{W}", us, nbytes=s["ff"] * W + T * W * 2 + T * 2 * s["ff"] * 2, flops=2.0 * T * 2 * s["ff"] * W)
+    return rows
+
+
+def run(args, peaks, clock_sampler_cls) -> dict:
+    import torch
+    from . import ops
+    from .build import build_library
+    from .model import QSpecLlamaConfig, QSpecLlamaModel
+    from .mutusun import MutusunConfig, MutusunModel, random_weights
+    from .scheduler import Scheduler
+    build_library()
+    torch.cuda.set_device(0)
+    hbm_gbs, bf16_tflops, peak_src = peaks
+    bf16_tflops = bf16_tflops or 1590.0
+    names = [n for n in (args.sizes.split(",") if args.sizes else SIZES) if n in SIZES]
+    steps, warmup = args.steps, max(3, args.warmup)
+    out = {}
+    sampler = clock_sampler_cls(0)
+    sampler.start()
+    l0 = ops.seq_launch_count()
+    for name in names:
+        s = SIZES[name]
+        res = {"layers": 4, "sizes": s}
+        cfgd = mutusun_config(s)
+        cfg = MutusunConfig.from_dict(cfgd)
+        model = MutusunModel(cfg, random_weights(cfg, 0), dtype=torch.bfloat16, device="cuda", n_slots=65, max_step_tokens=2048)
+        res["mutusun"] = {p: _throughput(torch, Scheduler(model, prefill_portion=p), VOCAB, 64, 300, 4096, p, steps, warmup) for p in (2048, 256)}
+        res["mutusun"]["state_bytes_per_sequence"] = model.state_bytes_per_slot()
+        del model
+        torch.cuda.empty_cache()
+        lc = QSpecLlamaConfig.llama3_8b(hidden_size=s["width"], intermediate_size=s["ff"], num_attention_heads=s["heads"],
+                                        num_key_value_heads=s["kv"], head_dim=s["dim"], num_hidden_layers=4, vocab_size=VOCAB,
+                                        max_seq_len=4096 + 8, name=f"int4-llama-{name}")
+        llama = QSpecLlamaModel(lc, max_batch=65, max_tokens=256, device="cuda")
+        res["int4_llama_w4a16"] = {256: _throughput(torch, Scheduler(llama, prefill_portion=256), VOCAB, 64, 300, 4096, 256, steps, warmup)}
+        res["int4_llama_w4a16"]["state_bytes_per_sequence"] = int(2 * llama.cache_k[:, 0].numel() * 2)
+        del llama
+        torch.cuda.empty_cache()
+        res["kernels"] = _kernel_table(torch, s, hbm_gbs, bf16_tflops)
+        res["like_kernels_int4_decoder"] = _like_kernels(torch, s, hbm_gbs, bf16_tflops)
+        out[name] = res
+    clocks = sampler.stop()
+    head = out[names[-1]]["mutusun"][2048]
+    return {"metric": "mutusun_prefill_decode_tokens_per_s", "value": head["decode_tokens_per_s"], "unit": "tokens/s (decode, 64 sequences)",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": head["decode_ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (float32 residual, norms, scores)", "data": "synthetic",
+            "config": {"design": "mutusun", "sizes": names, "weights": "random", "layers": 4,
+                       "l2": "kernel timings rotate buffers larger than the L2 where the kernel streams from HBM"},
+            "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src},
+            "gpu_launches": ops.seq_launch_count() - l0, "clocks": clocks, "results": out}

@@ -39,91 +39,155 @@ __global__ void __launch_bounds__(256) embed_kernel(const T* __restrict__ table,
 }
 
 // ---- residual + post-norm + pre-norm + short convolution ------------------------------------------------------
-// One CTA per token. The convolution needs the normalised rows of the previous taps-1 tokens: rows inside the step's
-// segment are recomputed from their inputs (two reductions per row; the rows are L2-resident), rows before it come from
-// the per-slot tail. Shared memory: taps rows of W floats.
-template <typename T>
+// A CTA walks over `run` consecutive tokens of the batch. The convolution needs the normalised rows of the previous
+// taps-1 tokens: rows inside the step's segment are kept in a shared-memory ring (the CTA first recomputes the taps-1
+// rows in front of its run), rows before the segment come from the per-slot tail. Every thread owns the same columns in
+// all rows, so the ring needs no barriers beyond those of the two row reductions. VEC = 4: 16-byte accesses (W % 4 == 0).
+template <int VEC> struct VecF { float v[VEC]; };
+template <int VEC> __device__ __forceinline__ VecF<VEC> ldv(const float* p) {
+  VecF<VEC> r;
+  if (VEC == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[1 % VEC] = t.y; r.v[2 % VEC] = t.z; r.v[3 % VEC] = t.w; }
+  else r.v[0] = *p;
+  return r;
+}
+template <int VEC> __device__ __forceinline__ VecF<VEC> ldv(const __nv_bfloat16* p) {
+  VecF<VEC> r;
+  if (VEC == 4) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    r.v[0] = a.x; r.v[1 % VEC] = a.y; r.v[2 % VEC] = b.x; r.v[3 % VEC] = b.y;
+  } else r.v[0] = __bfloat162float(*p);
+  return r;
+}
+template <int VEC> __device__ __forceinline__ void stv(float* p, const VecF<VEC>& r) {
+  if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1 % VEC], r.v[2 % VEC], r.v[3 % VEC]);
+  else *p = r.v[0];
+}
+template <int VEC> __device__ __forceinline__ void stv(__nv_bfloat16* p, const VecF<VEC>& r) {
+  if (VEC == 4) {
+    uint2 t;
+    *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(r.v[0], r.v[1 % VEC]);
+    *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(r.v[2 % VEC], r.v[3 % VEC]);
+    *reinterpret_cast<uint2*>(p) = t;
+  } else *p = __float2bfloat16_rn(r.v[0]);
+}
+
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 norm_conv_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const T* __restrict__ y, int y_parts,
                  long long y_part_stride, long long y_tok_stride, const float* __restrict__ y_w,
                  const float* __restrict__ post_w, const float* __restrict__ pre_w, const float* __restrict__ conv_w,
                  int taps, float* __restrict__ tail, int slots, T* __restrict__ out, const int* __restrict__ meta, int ntok,
-                 int W, float eps) {
+                 int W, float eps, int run) {
   pdl_enter();
-  extern __shared__ float sm_rows[];          // [taps][W]
+  extern __shared__ __align__(16) float sm_rows[];          // ring [rc][W]
   __shared__ float red[8];
-  const int i = blockIdx.x, tid = threadIdx.x;
-  const TokMeta m = load_meta(meta, ntok, i);
-  const int pos_start = m.pos - (i - m.seg_begin);
-  const int hist = taps - 1;
-  const size_t tail_buf = (size_t)slots * hist * W;
-  const float* tail_rd = tail ? tail + (size_t)m.phase * tail_buf + (size_t)m.slot * hist * W : nullptr;
-  float* tail_wr = tail ? tail + (size_t)(1 - m.phase) * tail_buf + (size_t)m.slot * hist * W : nullptr;
+  const int tid = threadIdx.x;
+  const int i0 = blockIdx.x * run, i1 = min(i0 + run, ntok);
+  const int rc = (conv_w && out) ? taps : 1, hist = rc - 1;
   const float inv_w = 1.0f / (float)W;
-  const int rows = (conv_w && out) ? taps : 1;
+  const size_t tail_buf = (size_t)slots * hist * W;
+  const int first_seg = meta[2 * ntok + i0];
+  const int u0 = hist > 0 ? max(first_seg, i0 - hist) : i0;
 
-  for (int j = 0; j < rows; ++j) {
-    float* hrow = sm_rows + (size_t)j * W;
-    const int u = i - j;
-    if (u >= m.seg_begin) {
-      const float* xr = x_in + (size_t)u * W;
-      if (y) {
-        float ss = 0.f;
-        for (int c = tid; c < W; c += 256) {
-          float v = 0.f;
-          for (int p = 0; p < y_parts; ++p) {
-            const float e = to_f(y[(size_t)u * y_tok_stride + (size_t)p * y_part_stride + c]);
-            v += y_w ? y_w[(size_t)u * y_parts + p] * e : e;
+  for (int u = u0; u < i1; ++u) {
+    float* hrow = sm_rows + (size_t)(u % rc) * W;
+    const float* xr = x_in + (size_t)u * W;
+    const bool own = u >= i0;
+    if (y) {
+      float ss = 0.f;
+      for (int c = tid * VEC; c < W; c += 256 * VEC) {
+        VecF<VEC> v;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v.v[e] = 0.f;
+        for (int p = 0; p < y_parts; ++p) {
+          const VecF<VEC> e = ldv<VEC>(y + (size_t)u * y_tok_stride + (size_t)p * y_part_stride + c);
+          const float pw = y_w ? y_w[(size_t)u * y_parts + p] : 1.0f;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) v.v[k] += pw * e.v[k];
+        }
+        stv<VEC>(hrow + c, v);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) ss += v.v[k] * v.v[k];
+      }
+      const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
+      for (int c = tid * VEC; c < W; c += 256 * VEC) {
+        const VecF<VEC> xv = ldv<VEC>(xr + c), yv = ldv<VEC>(hrow + c), pw = ldv<VEC>(post_w + c);
+        VecF<VEC> v;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v.v[k] = xv.v[k] + yv.v[k] * r * (1.0f + pw.v[k]);
+        stv<VEC>(hrow + c, v);
+        if (own) stv<VEC>(x_out + (size_t)u * W + c, v);
+      }
+    } else {
+      for (int c = tid * VEC; c < W; c += 256 * VEC) {
+        const VecF<VEC> v = ldv<VEC>(xr + c);
+        stv<VEC>(hrow + c, v);
+        if (own && x_out && x_out != x_in) stv<VEC>(x_out + (size_t)u * W + c, v);
+      }
+    }
+    if (!out) continue;
+    float ss = 0.f;
+    for (int c = tid * VEC; c < W; c += 256 * VEC) {
+      const VecF<VEC> v = ldv<VEC>(hrow + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) ss += v.v[k] * v.v[k];
+    }
+    const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
+    for (int c = tid * VEC; c < W; c += 256 * VEC) {
+      VecF<VEC> v = ldv<VEC>(hrow + c);
+      const VecF<VEC> pw = ldv<VEC>(pre_w + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v.v[k] = v.v[k] * r * (1.0f + pw.v[k]);
+      stv<VEC>(hrow + c, v);
+    }
+    if (!own) continue;
+    // ---- token u: convolution over its own row and the taps-1 before it, then the tail
+    const TokMeta m = load_meta(meta, ntok, u);
+    const int pos_start = m.pos - (u - m.seg_begin);
+    const float* tail_rd = tail ? tail + (size_t)m.phase * tail_buf + (size_t)m.slot * hist * W : nullptr;
+    float* tail_wr = tail ? tail + (size_t)(1 - m.phase) * tail_buf + (size_t)m.slot * hist * W : nullptr;
+    for (int c = tid * VEC; c < W; c += 256 * VEC) {
+      const VecF<VEC> h0 = ldv<VEC>(hrow + c);
+      VecF<VEC> v = h0;
+      if (conv_w) {
+        for (int j = 0; j < taps; ++j) {
+          VecF<VEC> src;
+          const int uu = u - j;
+          if (uu >= m.seg_begin) src = ldv<VEC>(sm_rows + (size_t)(uu % rc) * W + c);
+          else {
+            const int pu = m.pos - j;
+            if (pu >= 0 && tail_rd) src = ldv<VEC>(tail_rd + (size_t)(pu - (pos_start - hist)) * W + c);
+            else {
+#pragma unroll
+              for (int k = 0; k < VEC; ++k) src.v[k] = 0.f;
+            }
           }
-          hrow[c] = v;
-          ss += v * v;
-        }
-        const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
-        for (int c = tid; c < W; c += 256) {
-          const float v = xr[c] + hrow[c] * r * (1.0f + post_w[c]);
-          hrow[c] = v;
-          if (j == 0) x_out[(size_t)i * W + c] = v;
-        }
-      } else {
-        for (int c = tid; c < W; c += 256) {
-          const float v = xr[c];
-          hrow[c] = v;
-          if (j == 0 && x_out != x_in && x_out) x_out[(size_t)i * W + c] = v;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) v.v[k] += conv_w[(size_t)(c + k) * taps + (taps - 1 - j)] * src.v[k];
         }
       }
-      if (!out) return;
-      float ss = 0.f;
-      for (int c = tid; c < W; c += 256) ss += hrow[c] * hrow[c];
-      const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
-      for (int c = tid; c < W; c += 256) hrow[c] = hrow[c] * r * (1.0f + pre_w[c]);
-    } else {
-      const int pu = m.pos - j;                               // position of the wanted row, before the segment
-      const int r = pu - (pos_start - hist);                  // its row in the tail
-      for (int c = tid; c < W; c += 256) hrow[c] = (pu >= 0 && tail_rd) ? tail_rd[(size_t)r * W + c] : 0.f;
+      stv<VEC>(out + (size_t)u * W + c, v);
     }
-  }
-  __syncthreads();
-  for (int c = tid; c < W; c += 256) {
-    float v = sm_rows[c];
-    if (conv_w) {
-      float acc = 0.f;
-      for (int j = 0; j < taps; ++j) acc += conv_w[(size_t)c * taps + (taps - 1 - j)] * sm_rows[(size_t)j * W + c];
-      v += acc;
-    }
-    out[(size_t)i * W + c] = from_f<T>(v);
-  }
-  if (!tail_wr || hist == 0) return;
-  // new tail row r holds position pos_end - hist + r
-  const int pos_end = pos_start + (m.seg_end - m.seg_begin);
-  const int my_row = m.pos - (pos_end - hist);
-  if (my_row >= 0)
-    for (int c = tid; c < W; c += 256) tail_wr[(size_t)my_row * W + c] = sm_rows[c];
-  if (i == m.seg_begin) {                                     // rows older than the segment are carried over
-    for (int r = 0; r < hist; ++r) {
-      const int p = pos_end - hist + r;
-      if (p >= pos_start) break;
-      const int ro = p - (pos_start - hist);
-      for (int c = tid; c < W; c += 256) tail_wr[(size_t)r * W + c] = p >= 0 ? tail_rd[(size_t)ro * W + c] : 0.f;
+    if (!tail_wr || hist == 0) continue;
+    const int pos_end = pos_start + (m.seg_end - m.seg_begin);    // new tail row r holds position pos_end - hist + r
+    const int my_row = m.pos - (pos_end - hist);
+    if (my_row >= 0)
+      for (int c = tid * VEC; c < W; c += 256 * VEC) stv<VEC>(tail_wr + (size_t)my_row * W + c, ldv<VEC>(hrow + c));
+    if (u == m.seg_begin) {                                       // rows older than the segment are carried over
+      for (int r2 = 0; r2 < hist; ++r2) {
+        const int p = pos_end - hist + r2;
+        if (p >= pos_start) break;
+        const int ro = p - (pos_start - hist);
+        for (int c = tid * VEC; c < W; c += 256 * VEC) {
+          VecF<VEC> v;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) v.v[k] = 0.f;
+          if (p >= 0) v = ldv<VEC>(tail_rd + (size_t)ro * W + c);
+          stv<VEC>(tail_wr + (size_t)r2 * W + c, v);
+        }
+      }
     }
   }
 }
@@ -157,11 +221,144 @@ __device__ __forceinline__ float capped_sigmoid_weight(float dot, float scale, f
   return 1.0f / (1.0f + expf(-(s + bias)));
 }
 
+// One CTA (4 warps) per (token, key/value head): the H/G query heads that share the key/value head are served together,
+// so that every key and value row is fetched once per token. Keys and values go through shared memory in blocks of 32
+// rows, in their storage type, one 32-bit word per lane (two bfloat16 or one float32: coalesced loads, conflict-free
+// stores); the next block is fetched into registers while the current one is used. Scores: one lane per key (rows padded
+// to an odd number of words); weighted sum of values: one thread per output word.
+constexpr int ATT_KB = 32;       // keys per block
+constexpr int ATT_CH = 4;        // 32-word column chunks per row: D, DV <= 128 words (256 bfloat16 / 128 float32)
+constexpr int ATT_MAXW = 8;      // output words per thread: (H/G) * DV words <= 128 * ATT_MAXW
+
+template <typename T> struct AttWord;
+template <> struct AttWord<float> {
+  static constexpr int N = 1;
+  static __device__ __forceinline__ void get(uint32_t w, float& a, float& b) { a = __uint_as_float(w); b = 0.f; }
+  static __device__ __forceinline__ uint32_t put(float a, float) { return __float_as_uint(a); }
+};
+template <> struct AttWord<__nv_bfloat16> {
+  static constexpr int N = 2;
+  static __device__ __forceinline__ void get(uint32_t w, float& a, float& b) {
+    a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ uint32_t put(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 chunk_attn_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ ck, const T* __restrict__ cv,
                   const float* __restrict__ bias, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G,
                   int D, int DV, int size, float scale, float softcap) {
+  pdl_enter();
+  constexpr int WPE = AttWord<T>::N;
+  extern __shared__ __align__(16) unsigned char sm_att_raw[];
+  const int rep = H / G;
+  const int kw = D / WPE, vw = DV / WPE;      // words per key / value row
+  const int kst = kw | 1;                     // odd row stride: lanes that read different rows hit different banks
+  float* sq = reinterpret_cast<float*>(sm_att_raw);          // [rep][D]
+  float* sw = sq + rep * D;                                   // [rep][32]
+  uint32_t* sk = reinterpret_cast<uint32_t*>(sw + rep * ATT_KB);   // [32][kst]
+  uint32_t* sv = sk + ATT_KB * kst;                           // [32][vw]
+  const int i = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const TokMeta m = load_meta(meta, ntok, i);
+  const int pos_start = m.pos - (i - m.seg_begin);
+  const int lo = (m.pos / size) * size;
+  const int nkeys = m.pos - lo + 1;
+  const int koff = H * D + g * D, voff = H * D + G * D + g * DV;
+  for (int c = tid; c < rep * D; c += 128) sq[c] = to_f(qkv[(size_t)i * ld + (size_t)g * rep * D + c]);
+
+  uint32_t pk[8][ATT_CH], pv[8][ATT_CH];     // this warp's 8 rows of the block in flight
+  auto fetch = [&](int kb) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int jj = kb + warp + 4 * q;
+      const bool ok = jj < nkeys;
+      const int pj = lo + jj;
+      const bool fresh = pj >= pos_start;
+      const size_t brow = (size_t)(m.seg_begin + pj - pos_start) * ld;
+      const size_t crow = (size_t)m.slot * size + jj;
+      const uint32_t* kp = reinterpret_cast<const uint32_t*>(fresh ? qkv + brow + koff : ck + (crow * G + g) * D);
+      const uint32_t* vp = reinterpret_cast<const uint32_t*>(fresh ? qkv + brow + voff : cv + (crow * G + g) * DV);
+#pragma unroll
+      for (int ch = 0; ch < ATT_CH; ++ch) {
+        const int w = ch * 32 + lane;
+        pk[q][ch] = (ok && w < kw) ? __ldg(kp + w) : 0u;
+        pv[q][ch] = (ok && w < vw) ? __ldg(vp + w) : 0u;
+      }
+    }
+  };
+  float acc[ATT_MAXW][2];
+#pragma unroll
+  for (int k = 0; k < ATT_MAXW; ++k) acc[k][0] = acc[k][1] = 0.f;
+  const int nout_w = rep * vw;
+  fetch(0);
+  for (int kb = 0; kb < nkeys; kb += ATT_KB) {
+    __syncthreads();                          // the previous block has been consumed (and q is in place)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int r = warp + 4 * q;
+#pragma unroll
+      for (int ch = 0; ch < ATT_CH; ++ch) {
+        const int w = ch * 32 + lane;
+        if (w < kw) sk[r * kst + w] = pk[q][ch];
+        if (w < vw) sv[r * vw + w] = pv[q][ch];
+      }
+    }
+    __syncthreads();
+    if (kb + ATT_KB < nkeys) fetch(kb + ATT_KB);
+    for (int hh = warp; hh < rep; hh += 4) {
+      float w = 0.f;
+      if (kb + lane < nkeys) {
+        const uint32_t* kr = sk + lane * kst;
+        const float* qr = sq + hh * D;
+        float d0 = 0.f, d1 = 0.f;
+        for (int c = 0; c < kw; ++c) {
+          float a, b;
+          AttWord<T>::get(kr[c], a, b);
+          d0 += qr[c * WPE] * a;
+          if (WPE == 2) d1 += qr[c * WPE + 1] * b;
+        }
+        w = capped_sigmoid_weight(d0 + d1, scale, softcap, bias[g * rep + hh]);
+      }
+      sw[hh * ATT_KB + lane] = w;
+    }
+    __syncthreads();
+    const int nk = min(ATT_KB, nkeys - kb);
+#pragma unroll
+    for (int k = 0; k < ATT_MAXW; ++k) {
+      const int o = tid + k * 128;
+      if (o < nout_w) {
+        const int hh = o / vw, dw = o - hh * vw;
+        const float* wr = sw + hh * ATT_KB;
+        float a0 = acc[k][0], a1 = acc[k][1];
+        for (int r = 0; r < nk; ++r) {
+          float a, b;
+          AttWord<T>::get(sv[r * vw + dw], a, b);
+          a0 += wr[r] * a;
+          a1 += wr[r] * b;
+        }
+        acc[k][0] = a0; acc[k][1] = a1;
+      }
+    }
+  }
+  uint32_t* op = reinterpret_cast<uint32_t*>(out + (size_t)i * H * DV + (size_t)g * rep * DV);
+#pragma unroll
+  for (int k = 0; k < ATT_MAXW; ++k) {
+    const int o = tid + k * 128;
+    if (o < nout_w) op[o] = AttWord<T>::put(acc[k][0], acc[k][1]);
+  }
+}
+
+// The same for rows that cannot be read as 32-bit words (odd head sizes or leading dimensions in bfloat16): one CTA per
+// (token, query head), element by element.
+template <typename T>
+__global__ void __launch_bounds__(128)
+chunk_attn_plain_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ ck, const T* __restrict__ cv,
+                        const float* __restrict__ bias, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G,
+                        int D, int DV, int size, float scale, float softcap) {
   pdl_enter();
   extern __shared__ float sm_att[];           // q [D] | weights [size]
   float* sq = sm_att;
@@ -380,19 +577,22 @@ extern "C" int qspec_seq_embed(const void* table, const int* ids, float* x, int 
   return QSPEC_OK;
 }
 
-template <typename T>
+template <typename T, int VEC>
 static int launch_norm_conv(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
                             long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
                             const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok, int W,
                             float eps, cudaStream_t st) {
   const size_t smem = (size_t)taps * W * sizeof(float);
+  QSPEC_REQUIRE(smem <= 200 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_norm_conv: %d taps x width %d exceed shared memory", taps, W);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    QSPEC_CUDA(cudaFuncSetAttribute(norm_conv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    QSPEC_CUDA((cudaFuncSetAttribute(norm_conv_kernel<T, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)));
     configured = smem;
   }
-  launch_pdl(norm_conv_kernel<T>, dim3(ntok), dim3(256), smem, st, x_in, x_out, (const T*)y, y_parts, y_part_stride, y_tok_stride,
-             y_w, post_w, pre_w, conv_w, taps, tail, slots, (T*)out, meta, ntok, W, eps);
+  // tokens per CTA: one while the batch is small (latency), a run of four once there are CTAs to spare
+  const int run = ntok >= 1024 ? 4 : 1;
+  launch_pdl(norm_conv_kernel<T, VEC>, dim3((ntok + run - 1) / run), dim3(256), smem, st, x_in, x_out, (const T*)y, y_parts,
+             y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps, tail, slots, (T*)out, meta, ntok, W, eps, run);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
@@ -413,11 +613,14 @@ extern "C" int qspec_seq_norm_conv(const float* x_in, float* x_out, const void* 
   SEQ_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
   if (!conv_w) tail = nullptr;
-  if (dtype == QSPEC_DTYPE_F32)
-    return launch_norm_conv<float>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps, tail,
-                                   slots, out, meta, ntok, W, eps, (cudaStream_t)stream);
-  return launch_norm_conv<__nv_bfloat16>(x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps,
-                                         tail, slots, out, meta, ntok, W, eps, (cudaStream_t)stream);
+  // 16-byte accesses when every row starts on a 16-byte boundary
+  const bool al = W % 4 == 0 && y_part_stride % 4 == 0 && y_tok_stride % 4 == 0 &&
+                  (((uintptr_t)x_in | (uintptr_t)x_out | (uintptr_t)y | (uintptr_t)out | (uintptr_t)tail | (uintptr_t)post_w |
+                    (uintptr_t)pre_w) & 15) == 0;
+#define NC_ARGS x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps, tail, slots, out, meta, ntok, W, eps, (cudaStream_t)stream
+  if (dtype == QSPEC_DTYPE_F32) return al ? launch_norm_conv<float, 4>(NC_ARGS) : launch_norm_conv<float, 1>(NC_ARGS);
+  return al ? launch_norm_conv<__nv_bfloat16, 4>(NC_ARGS) : launch_norm_conv<__nv_bfloat16, 1>(NC_ARGS);
+#undef NC_ARGS
 }
 
 extern "C" int qspec_seq_qk_norm(void* qkv, int ld, const float* q_w, const float* k_w, int ntok, int H, int G, int D, float eps,
@@ -453,22 +656,49 @@ extern "C" int qspec_seq_chunk_attention(const void* qkv, int ld, const void* ca
   QSPEC_REQUIRE(bias && out, QSPEC_ERR_INVALID_ARG, "seq_chunk_attention: null pointer");
   SEQ_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
+  const int rep = H / G;
+  const int wpe = dtype == QSPEC_DTYPE_F32 ? 1 : 2;
+  const int w = dtype == QSPEC_DTYPE_F32 ? 0 : 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  // word form: every row readable as 32-bit words, a row within ATT_CH chunks, the outputs within the per-thread budget
+  const bool words = D % wpe == 0 && DV % wpe == 0 && ld % wpe == 0 && D / wpe <= 32 * ATT_CH && DV / wpe <= 32 * ATT_CH &&
+                     (long long)rep * (DV / wpe) <= 128 * ATT_MAXW && (H * DV) % wpe == 0 &&
+                     (((uintptr_t)qkv | (uintptr_t)cache_k | (uintptr_t)cache_v | (uintptr_t)out) & 3) == 0;
+  if (words) {
+    const int kst = (D / wpe) | 1;
+    const size_t smem = (size_t)(rep * D + rep * ATT_KB) * sizeof(float) + (size_t)ATT_KB * (kst + DV / wpe) * 4;
+    QSPEC_REQUIRE(smem <= 200 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_chunk_attention: %d query heads of size %d per key/value head do not fit shared memory", rep, D);
+    static size_t configured[2] = {0, 0};
+    if (smem > 48 * 1024 && smem > configured[w]) {
+      if (w == 0) QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      else QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      configured[w] = smem;
+    }
+    if (w == 0)
+      launch_pdl(chunk_attn_kernel<float>, dim3(ntok, G), dim3(128), smem, st, (const float*)qkv, ld, (const float*)cache_k,
+                 (const float*)cache_v, bias, (float*)out, meta, ntok, H, G, D, DV, size, scale, softcap);
+    else
+      launch_pdl(chunk_attn_kernel<__nv_bfloat16>, dim3(ntok, G), dim3(128), smem, st, (const __nv_bfloat16*)qkv, ld,
+                 (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, bias, (__nv_bfloat16*)out, meta, ntok, H, G, D, DV,
+                 size, scale, softcap);
+    QSPEC_CHECK_LAUNCH(1);
+    return QSPEC_OK;
+  }
   const size_t smem = (size_t)(D + size) * sizeof(float);
   QSPEC_REQUIRE(smem <= 200 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_chunk_attention: chunk of %d keys does not fit shared memory", size);
-  static size_t configured[2] = {0, 0};
-  const int w = dtype == QSPEC_DTYPE_F32 ? 0 : 1;
-  if (smem > 48 * 1024 && smem > configured[w]) {
-    if (w == 0) QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    else QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[w] = smem;
+  static size_t configured_plain[2] = {0, 0};
+  if (smem > 48 * 1024 && smem > configured_plain[w]) {
+    if (w == 0) QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_plain_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    else QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_plain_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured_plain[w] = smem;
   }
   if (w == 0)
-    launch_pdl(chunk_attn_kernel<float>, dim3(ntok, H), dim3(128), smem, (cudaStream_t)stream, (const float*)qkv, ld,
-               (const float*)cache_k, (const float*)cache_v, bias, (float*)out, meta, ntok, H, G, D, DV, size, scale, softcap);
+    launch_pdl(chunk_attn_plain_kernel<float>, dim3(ntok, H), dim3(128), smem, st, (const float*)qkv, ld, (const float*)cache_k,
+               (const float*)cache_v, bias, (float*)out, meta, ntok, H, G, D, DV, size, scale, softcap);
   else
-    launch_pdl(chunk_attn_kernel<__nv_bfloat16>, dim3(ntok, H), dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, ld,
-               (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, bias, (__nv_bfloat16*)out, meta, ntok, H, G, D, DV, size,
-               scale, softcap);
+    launch_pdl(chunk_attn_plain_kernel<__nv_bfloat16>, dim3(ntok, H), dim3(128), smem, st, (const __nv_bfloat16*)qkv, ld,
+               (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, bias, (__nv_bfloat16*)out, meta, ntok, H, G, D, DV,
+               size, scale, softcap);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }

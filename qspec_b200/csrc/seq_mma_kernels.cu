@@ -207,11 +207,14 @@ static int launch_attn_mma(const void* qkv, int ld, const void* ck, const void* 
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Grouped expert feed-forward. (1) moe_group_kernel sorts the (token, choice) pairs by expert and lists the 64-row tiles;
+// Grouped expert feed-forward. (1) moe_group_kernel sorts the (token, choice) pairs by expert and lists the 128-row tiles;
 // (2) grouped_gemm_kernel<true>: [gate ; up] products of the gathered token rows, clamped-gated activation, Y rows in
 // sorted order; (3) grouped_gemm_kernel<false>: down products, rows scattered back to out[token, choice]. Pairs whose
 // choice is an identity expert are copied by moe_identity_kernel.
 // ---------------------------------------------------------------------------------------------------------------------
+constexpr int GG_BM = 128, GG_BK = 64, GG_KP = GG_BK + 8, GG_STAGES = 3;   // rows per expert tile, k-step, padded smem row, ring depth
+constexpr size_t GG_SMEM = (size_t)GG_STAGES * 2 * 128 * GG_KP * sizeof(__nv_bfloat16);
+
 struct GroupPlan {
   int* offsets;      // [E + 1] first sorted row of every expert
   int* cursor;       // [E]
@@ -237,7 +240,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
     for (int e = 0; e < E; ++e) {
       const int c = s_cnt[e];
       p.offsets[e] = at;
-      for (int r = 0; r < c; r += 64) { p.tile_expert[nt] = e; p.tile_row0[nt] = at + r; ++nt; }
+      for (int r = 0; r < c; r += GG_BM) { p.tile_expert[nt] = e; p.tile_row0[nt] = at + r; ++nt; }
       s_cnt[e] = at;                      // becomes the cursor
       at += c;
     }
@@ -262,97 +265,140 @@ __global__ void __launch_bounds__(128) moe_identity_kernel(const bf16* __restric
   for (int c = threadIdx.x; c < W; c += 128) dst[c] = src[c];
 }
 
-// C[m, n] = sum_k A[row(m), k] * B_e[n, k] over the rows of one expert tile. 64 x 64 output tile, k-steps of 32, 4 warps
-// (16 rows each). DUAL: two B matrices (gate rows n and up rows F + n) and the activation epilogue.
+// C[m, n] = sum_k A[row(m), k] * B_e[n, k] over the rows of one expert tile. 128 rows x 128 B-rows per CTA, k-steps of
+// 64 through a three-stage cp.async ring, 8 warps as 2 (rows) x 4 (columns), fragments by ldmatrix. DUAL: the 128 B-rows are
+// 64 gate rows and the 64 up rows of the same columns, every warp holds both for its 16 columns, and the epilogue applies
+// the clamped-gated activation; otherwise 128 consecutive output columns.
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int n = valid ? 16 : 0;                         // 0: the 16 bytes are zero-filled, the source is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
 template <bool DUAL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 grouped_gemm_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, GroupPlan p, int K, int N, int top,
                     float limit) {
   pdl_enter();
-  constexpr int KP = 32 + 8;
-  __shared__ __align__(16) bf16 sA[64 * KP];
-  __shared__ __align__(16) bf16 sB[(DUAL ? 2 : 1) * 64 * KP];
-  __shared__ int s_row[64];
+  extern __shared__ __align__(16) unsigned char gg_smem[];
+  bf16 (*sA)[GG_BM * GG_KP] = reinterpret_cast<bf16 (*)[GG_BM * GG_KP]>(gg_smem);
+  bf16 (*sB)[128 * GG_KP] = reinterpret_cast<bf16 (*)[128 * GG_KP]>(gg_smem + (size_t)GG_STAGES * GG_BM * GG_KP * sizeof(bf16));
+  __shared__ int s_row[GG_BM];
   const int tile = blockIdx.x;
   if (tile >= *p.ntiles) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int wm = warp >> 2, wn = warp & 3;
   const int e = p.tile_expert[tile], m0 = p.tile_row0[tile];
   const int mend = p.offsets[e + 1];
-  const int n0 = blockIdx.y * 64;
-  if (tid < 64) {
+  constexpr int BN = DUAL ? 64 : 128;                    // output columns per CTA
+  const int n0 = blockIdx.y * BN;
+  if (tid < GG_BM) {
     const int m = m0 + tid;
     s_row[tid] = m < mend ? p.perm[m] : -1;
   }
   __syncthreads();
   const bf16* Be = B + (size_t)e * (DUAL ? 2 : 1) * N * K;
-  float acc[DUAL ? 2 : 1][8][4];
+  // this thread's four A vectors and four B vectors of a stage
+  constexpr int NV = GG_BM * (GG_BK / 8) / 256, VPR = GG_BK / 8;
+  const bf16* a_src[NV];
+  const bf16* b_src[NV];
+  bool a_ok[NV], b_ok[NV];
+  int a_dst[NV], b_dst[NV];
 #pragma unroll
-  for (int d = 0; d < (DUAL ? 2 : 1); ++d)
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt) acc[d][nt][0] = acc[d][nt][1] = acc[d][nt][2] = acc[d][nt][3] = 0.f;
-
-  for (int k0 = 0; k0 < K; k0 += 32) {
-    __syncthreads();
-    for (int v = tid; v < 64 * 4; v += 128) {
-      const int r = v >> 2, c = (v & 3) * 8;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      const int pr = s_row[r];
-      if (pr >= 0 && k0 + c < K) {
-        const bf16* src = DUAL ? A + (size_t)(pr / top) * K : A + (size_t)(m0 + r) * K;
-        val = *reinterpret_cast<const uint4*>(src + k0 + c);
-      }
-      *reinterpret_cast<uint4*>(sA + r * KP + c) = val;
-    }
-    for (int v = tid; v < (DUAL ? 2 : 1) * 64 * 4; v += 128) {
-      const int d = v / 256, r = (v % 256) >> 2, c = (v & 3) * 8;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (n0 + r < N && k0 + c < K) val = *reinterpret_cast<const uint4*>(Be + ((size_t)d * N + n0 + r) * K + k0 + c);
-      *reinterpret_cast<uint4*>(sB + (d * 64 + r) * KP + c) = val;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
-      uint32_t a[4];
-      const bf16* ap = sA + (warp * 16 + gid) * KP + ks * 16 + tig * 2;
-      a[0] = *reinterpret_cast<const uint32_t*>(ap);
-      a[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * KP);
-      a[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * KP + 8);
-#pragma unroll
-      for (int d = 0; d < (DUAL ? 2 : 1); ++d)
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          const bf16* bp = sB + (d * 64 + nt * 8 + gid) * KP + ks * 16 + tig * 2;
-          mma_bf16_16816(acc[d][nt], a, *reinterpret_cast<const uint32_t*>(bp), *reinterpret_cast<const uint32_t*>(bp + 8));
-        }
-    }
-  }
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = warp * 16 + gid + half * 8;
+  for (int q = 0; q < NV; ++q) {
+    const int v = tid + q * 256, r = v / VPR, c = (v % VPR) * 8;
     const int pr = s_row[r];
-    if (pr < 0) continue;
-    bf16* crow = DUAL ? C + (size_t)(m0 + r) * N : C + (size_t)pr * N;
+    a_ok[q] = pr >= 0;
+    a_src[q] = (DUAL ? A + (size_t)(pr < 0 ? 0 : pr / top) * K : A + (size_t)(m0 + r) * K) + c;
+    if (!a_ok[q]) a_src[q] = A;
+    a_dst[q] = r * GG_KP + c;
+    int brow;                                            // row of B_e this smem row holds
+    if (DUAL) brow = (r < 64 ? 0 : N) + n0 + (r & 63);
+    else brow = n0 + r;
+    b_ok[q] = (DUAL ? n0 + (r & 63) : n0 + r) < N;
+    b_src[q] = b_ok[q] ? Be + (size_t)brow * K + c : Be;
+    b_dst[q] = r * GG_KP + c;
+  }
+  auto issue = [&](int stage, int k0) {
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int n = n0 + nt * 8 + tig * 2;
-      float v0, v1;
-      if (DUAL) {
-        // projections leave the matrix unit in bfloat16, like the dense layers' products
-        float gq0 = fminf(__bfloat162float(__float2bfloat16_rn(acc[0][nt][half * 2])), limit);
-        float gq1 = fminf(__bfloat162float(__float2bfloat16_rn(acc[0][nt][half * 2 + 1])), limit);
-        float uq0 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(acc[DUAL ? 1 : 0][nt][half * 2])), -limit), limit);
-        float uq1 = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(acc[DUAL ? 1 : 0][nt][half * 2 + 1])), -limit), limit);
-        v0 = gq0 * (1.0f / (1.0f + expf(-1.702f * gq0))) * (uq0 + 1.0f);
-        v1 = gq1 * (1.0f / (1.0f + expf(-1.702f * gq1))) * (uq1 + 1.0f);
-      } else {
-        v0 = acc[0][nt][half * 2];
-        v1 = acc[0][nt][half * 2 + 1];
+    for (int q = 0; q < NV; ++q) {
+      const bool in_k = k0 + (((tid + q * 256) % VPR) * 8) < K;
+      cp_async16(&sA[stage][a_dst[q]], a_src[q] + ((a_ok[q] && in_k) ? k0 : 0), a_ok[q] && in_k);
+      cp_async16(&sB[stage][b_dst[q]], b_src[q] + ((b_ok[q] && in_k) ? k0 : 0), b_ok[q] && in_k);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  float acc[4][4][4];
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
+  // B rows of this warp's four n-tiles (pairs of tiles are 16 consecutive rows)
+  const int brow0 = DUAL ? 16 * wn : 32 * wn;            // tiles 0, 1
+  const int brow1 = DUAL ? 64 + 16 * wn : 32 * wn + 16;  // tiles 2, 3
+  const int nk = (K + GG_BK - 1) / GG_BK;
+  // ring: stage kt lives in slot kt % 3; two stages are in flight while one is multiplied. Past the end of K the copies
+  // are zero-size (nothing is read), so every iteration commits exactly one group and the wait count stays fixed.
+  issue(0, 0);
+  issue(1, GG_BK);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int st = kt % GG_STAGES;
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    __syncthreads();                                     // stage kt has landed for everyone; slot (kt + 2) % 3 is free
+    issue((kt + 2) % GG_STAGES, (kt + 2) * GG_BK);
+#pragma unroll
+    for (int ks = 0; ks < GG_BK / 16; ++ks) {
+      uint32_t bfr[2][4];
+      const int brl = (lane & 7) + ((lane >> 4) << 3), bcl = ks * 16 + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(bfr[0], &sB[st][(brow0 + brl) * GG_KP + bcl]);
+      ldmatrix_x4(bfr[1], &sB[st][(brow1 + brl) * GG_KP + bcl]);
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        uint32_t af[4];
+        ldmatrix_x4(af, &sA[st][(wm * 64 + mt * 16 + (lane & 15)) * GG_KP + ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) mma_bf16_16816(acc[mt][nt], af, bfr[nt >> 1][(nt & 1) * 2], bfr[nt >> 1][(nt & 1) * 2 + 1]);
       }
-      if (n + 1 < N) *reinterpret_cast<uint32_t*>(crow + n) = pack_bf2(v0, v1);
-      else if (n < N) crow[n] = __float2bfloat16_rn(v0);
     }
   }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+#pragma unroll
+  for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 64 + mt * 16 + gid + half * 8;
+      const int pr = s_row[r];
+      if (pr < 0) continue;
+      bf16* crow = DUAL ? C + (size_t)(m0 + r) * N : C + (size_t)pr * N;
+      if (DUAL) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int n = n0 + 16 * wn + nt * 8 + tig * 2;
+          float v[2];
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            // projections leave the matrix unit in bfloat16, like the dense layers' products
+            const float gq = fminf(__bfloat162float(__float2bfloat16_rn(acc[mt][nt][half * 2 + x])), limit);
+            const float uq = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(acc[mt][nt + 2][half * 2 + x])), -limit), limit);
+            v[x] = gq * (1.0f / (1.0f + expf(-1.702f * gq))) * (uq + 1.0f);
+          }
+          if (n + 1 < N) *reinterpret_cast<uint32_t*>(crow + n) = pack_bf2(v[0], v[1]);
+          else if (n < N) crow[n] = __float2bfloat16_rn(v[0]);
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int n = n0 + 32 * wn + nt * 8 + tig * 2;
+          if (n + 1 < N) *reinterpret_cast<uint32_t*>(crow + n) = pack_bf2(acc[mt][nt][half * 2], acc[mt][nt][half * 2 + 1]);
+          else if (n < N) crow[n] = __float2bfloat16_rn(acc[mt][nt][half * 2]);
+        }
+      }
+    }
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -385,7 +431,7 @@ extern "C" int qspec_seq_chunk_attention_mma(const void* qkv, int ld, const void
 extern "C" int qspec_moe_expert_grouped_supported(int W, int F) { return W > 0 && F > 0 && W % 8 == 0 && F % 8 == 0; }
 
 static size_t grouped_layout(int ntok, int top, int E, int F, size_t* off) {
-  const size_t npairs = (size_t)ntok * top, max_tiles = npairs / 64 + E + 1;
+  const size_t npairs = (size_t)ntok * top, max_tiles = npairs / 128 + E + 1;
   size_t at = 0;
   off[0] = at; at = align_up(at + (size_t)(E + 1) * 4, 16);      // offsets
   off[1] = at; at = align_up(at + (size_t)(E + 1) * 4, 16);      // cursor (unused slot kept for alignment of the plan)
@@ -421,16 +467,22 @@ extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, cons
   p.tile_expert = (int*)(ws + off[3]); p.tile_row0 = (int*)(ws + off[4]); p.perm = (int*)(ws + off[5]);
   bf16* Y = (bf16*)(ws + off[6]);
   const int npairs = ntok * top;
-  const int max_tiles = npairs / 64 + E + 1;
+  const int max_tiles = npairs / 128 + E + 1;
   launch_pdl(moe_identity_kernel, dim3(npairs), dim3(128), 0, st, (const bf16*)h, idx, (bf16*)out, W, E, top);
   QSPEC_CHECK_LAUNCH(1);
   if (E == 0) return QSPEC_OK;
   launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), st, idx, npairs, E, p);
   QSPEC_CHECK_LAUNCH(1);
-  launch_pdl(grouped_gemm_kernel<true>, dim3(max_tiles, (F + 63) / 64), dim3(128), 0, st, (const bf16*)h, (const bf16*)gate_up, Y, p, W,
+  static bool configured = false;
+  if (!configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
+    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
+    configured = true;
+  }
+  launch_pdl(grouped_gemm_kernel<true>, dim3(max_tiles, (F + 63) / 64), dim3(256), GG_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y, p, W,
              F, top, limit);
   QSPEC_CHECK_LAUNCH(1);
-  launch_pdl(grouped_gemm_kernel<false>, dim3(max_tiles, (W + 63) / 64), dim3(128), 0, st, (const bf16*)Y, (const bf16*)down, (bf16*)out,
+  launch_pdl(grouped_gemm_kernel<false>, dim3(max_tiles, (W + 127) / 128), dim3(256), GG_SMEM, st, (const bf16*)Y, (const bf16*)down, (bf16*)out,
              p, F, W, top, limit);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;

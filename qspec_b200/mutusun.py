@@ -329,7 +329,9 @@ class MutusunModel(torch.nn.Module):
                     rw = self.buf_rw[:T * f.top].view(T, f.top)
                     pair = self.buf_pair[:T * f.top * W].view(T, f.top, W)
                     ops.moe_route(h, p.router, p.correction, idx, rw)
-                    if self.use_tiles and T >= self.tiles_min_tokens and ops.moe_expert_grouped_supported(h, f.ff):
+                    # grouped tiles once an expert sees several rows on average (its weights are then read once per tile,
+                    # not once per row); a handful of tokens stay with the row-per-CTA form
+                    if self.use_tiles and T * f.top >= 4 * max(f.experts, 1) and ops.moe_expert_grouped_supported(h, f.ff):
                         ops.moe_expert_grouped(h, p.gate_up, p.edown, idx, pair, f.experts, f.ff, f.limit)
                     else:
                         ops.moe_expert_tokens(h, p.gate_up, p.edown, idx, pair, f.experts, f.ff, f.limit)

@@ -36,7 +36,8 @@ def _dt(t: torch.Tensor) -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of the current stream of the current device, without building a torch.cuda.Stream object per launch
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 def _chk(t: Optional[torch.Tensor], name: str, dtypes=None, allow_none=False):

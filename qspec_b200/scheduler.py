@@ -66,13 +66,12 @@ class Scheduler:
                 held = self.table.pos[self.table.slot_of[rid]] if rid in self.table.slot_of else 0
                 if held + len(toks) > limit:
                     raise RuntimeError(f"request {rid!r} would hold {held + len(toks)} tokens; the cache takes {limit}")
-        n_want = sum(len(w) for _, _, w in entries)
-        out_rows: List[Tuple[int, int]] = []            # (output row, row of the pass) for the current pass
-        out = None
         base, offsets = 0, []
         for _, _, want in entries:
             offsets.append(base)
             base += len(want)
+        n_want = base
+        parts, order = [], []                           # logits per pass; the output row of every gathered row
         work = [(e, 0) for e in range(len(entries)) if len(entries[e][1])]
         while work:
             segs, rows, at, nxt, ids = [], [], 0, [], []
@@ -90,18 +89,23 @@ class Scheduler:
                 at += n
                 if done + n < len(toks):
                     nxt.append((e, done + n))
-            meta = self.table.plan(segs, ids)
+            rows.sort()
+            split = len(rows) > at                      # a token wanted more than once: gather through a tensor of its own
+            meta = self.table.plan(segs, ids, None if split else [r for _, r in rows])
             hidden = model.forward_batch(meta.ids, meta)
             self.table.commit(meta)
             if rows:
-                sel = torch.tensor([r for _, r in rows], dtype=torch.int64, device=model.device)
-                lg = model.logits(hidden.index_select(0, sel))
-                if out is None:
-                    out = torch.empty(n_want, lg.shape[1], dtype=lg.dtype, device=lg.device)
-                out.index_copy_(0, torch.tensor([o for o, _ in rows], dtype=torch.int64, device=lg.device), lg)
+                sel = torch.tensor([r for _, r in rows], dtype=torch.int32, device=model.device) if split else meta.rows
+                parts.append(model.logits(hidden.index_select(0, sel)))
+                order.extend(o for o, _ in rows)
             work = nxt
-        if out is None:
-            out = torch.empty(0, model.vocab_size, dtype=torch.float32, device=model.device)
+        if not parts:
+            return torch.empty(0, model.vocab_size, dtype=torch.float32, device=model.device)
+        out = parts[0] if len(parts) == 1 else torch.cat(parts, 0)
+        if order != sorted(order):                      # wanted lists out of order across passes: put the rows in place
+            inv = sorted(range(len(order)), key=order.__getitem__)
+            out = out.index_select(0, torch.tensor(inv, dtype=torch.int64, device=out.device))
+        assert out.shape[0] == n_want
         return out
 
     def release(self, rid: Hashable) -> None:

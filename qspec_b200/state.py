@@ -50,6 +50,7 @@ class BatchMeta:
     """One step's token table. `table` is the device int32 [5, ntok] the kernels read; the rest is host bookkeeping."""
     table: torch.Tensor
     ids: torch.Tensor                                  # device int32 [ntok]: the step's token ids (zeros if none were given)
+    rows: torch.Tensor                                 # device int32 [n]: batch rows the caller asked to have gathered
     ntok: int
     segments: List[Tuple[Hashable, int, int, int]]     # (request id, slot, first position, token count)
 
@@ -87,38 +88,50 @@ class SequenceTable:
     def held_tokens(self) -> int:
         return sum(self.pos[s] for s in self.slot_of.values())
 
-    def plan(self, segments: Sequence[Tuple[Hashable, int]], token_ids: Sequence[int] = None) -> BatchMeta:
+    def plan(self, segments: Sequence[Tuple[Hashable, int]], token_ids: Sequence[int] = None,
+             rows: Sequence[int] = None) -> BatchMeta:
         """segments: (request id, number of new tokens), each request at most once; unknown requests get a slot.
-        token_ids: the step's tokens in batch order; they travel to the device in the same copy as the table.
-        Every step stages its table in a fresh pinned block: the copy is asynchronous, and the host may plan the next
-        step before the device has fetched this one."""
-        ntok = sum(n for _, n in segments)
+        token_ids: the step's tokens in batch order; rows: batch rows a caller wants to gather afterwards (at most one
+        per token). Both travel to the device in the same copy as the table. Every step stages its table in a fresh
+        pinned block: the copy is asynchronous, and the host may plan the next step before the device has fetched this
+        one."""
+        import numpy as np
+        counts = np.fromiter((n for _, n in segments), dtype=np.int64, count=len(segments))
+        if len(counts) and counts.min() < 1:
+            raise ValueError("a segment needs at least one token")
+        ntok = int(counts.sum())
         if ntok > self.max_step_tokens:
             raise ValueError(f"a step of {ntok} tokens exceeds max_step_tokens = {self.max_step_tokens}")
         if token_ids is not None and len(token_ids) != ntok:
             raise ValueError(f"{len(token_ids)} token ids for a step of {ntok} tokens")
-        h = torch.zeros(META_ROWS + 1, ntok, dtype=torch.int32)
-        if token_ids is not None:
-            h[META_ROWS] = torch.as_tensor(token_ids, dtype=torch.int32)
-        at, segs = 0, []
+        if rows is not None and len(rows) > ntok:
+            raise ValueError("more rows to gather than tokens in the step")
+        slots, firsts, segs = [], [], []
         for rid, n in segments:
-            if n < 1:
-                raise ValueError("a segment needs at least one token")
             slot = self.slot_of[rid] if rid in self.slot_of else self.open(rid)
-            if any(s[1] == slot for s in segs):
-                raise ValueError(f"request {rid!r} appears twice in one step")
-            p0 = self.pos[slot]
-            h[0, at:at + n] = slot
-            h[1, at:at + n] = torch.arange(p0, p0 + n, dtype=torch.int32)
-            h[2, at:at + n] = at
-            h[3, at:at + n] = at + n
-            h[4, at:at + n] = self.phase[slot]
-            segs.append((rid, slot, p0, n))
-            at += n
+            slots.append(slot)
+            firsts.append(self.pos[slot])
+            segs.append((rid, slot, self.pos[slot], int(n)))
+        if len(set(slots)) != len(slots):
+            raise ValueError("a request appears twice in one step")
+        begin = np.cumsum(counts) - counts
+        h = np.zeros((META_ROWS + 2, ntok), dtype=np.int32)
+        h[0] = np.repeat(np.asarray(slots, dtype=np.int64), counts)
+        h[2] = np.repeat(begin, counts)
+        h[1] = np.repeat(np.asarray(firsts, dtype=np.int64), counts) + (np.arange(ntok) - h[2])
+        h[3] = np.repeat(begin + counts, counts)
+        h[4] = np.repeat(np.asarray([self.phase[s] for s in slots], dtype=np.int64), counts)
+        if token_ids is not None:
+            h[META_ROWS] = np.asarray(token_ids, dtype=np.int64)
+        nrows = 0
+        if rows is not None and len(rows):
+            nrows = len(rows)
+            h[META_ROWS + 1, :nrows] = np.asarray(rows, dtype=np.int64)
+        t = torch.from_numpy(h)
         if self.device.type == "cuda":
-            h = h.pin_memory()
-        dev = h.to(self.device, non_blocking=True)
-        return BatchMeta(table=dev[:META_ROWS], ids=dev[META_ROWS], ntok=ntok, segments=segs)
+            t = t.pin_memory()
+        dev = t.to(self.device, non_blocking=True)
+        return BatchMeta(table=dev[:META_ROWS], ids=dev[META_ROWS], rows=dev[META_ROWS + 1, :nrows], ntok=ntok, segments=segs)
 
     def commit(self, meta: BatchMeta) -> None:
         """The step described by `meta` has been queued: its tokens now count as consumed."""
