@@ -98,6 +98,13 @@ class MutusunConfig:
             else:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {f['kind']!r}")
             layers.append(LayerSpec(mixer=mixer, mlp=mlp, weights_of=int(e.get("weights_of", i))))
+        for i, l in enumerate(layers):                     # a borrowed layer may itself borrow: follow to the owner
+            j, hops = l.weights_of, 0
+            while layers[j].weights_of != j:
+                j, hops = layers[j].weights_of, hops + 1
+                if hops > len(layers):
+                    raise ValueError(f"layer {i}: weights_of forms a cycle")
+            l.weights_of = j
         canon = d.get("canon") or {}
         return MutusunConfig(vocab=int(d["vocab"]), width=int(d["width"]), eps=float(d["norm"]["eps"]),
                              taps=int(canon.get("taps") or 0), layers=layers)

@@ -273,6 +273,11 @@ CONFIGS = {
                   width=72, vocab=50, taps=2, eps=1e-6),
     "taps4": config([dict(mixer=mixer(size=9), mlp=moe(experts=2, identity=3, top=4)), dict(mixer=mixer(size=9), mlp=moe(experts=2, identity=3, top=4), weights_of=0)],
                     width=48, taps=4),
+    # nothing divisible by anything: odd head sizes and leading dimension (element-wise kernels), five taps, one kv head
+    "ragged": config([dict(mixer=mixer(heads=3, kv=1, dim=9, vdim=5, size=6, scale=0.4, cap=3.0), mlp=moe(ff=7, experts=3, identity=1, top=2)),
+                      dict(mixer=mixer(heads=2, kv=2, dim=10, vdim=6, size=11), mlp={"kind": "dense", "ff": 13}),
+                      dict(mixer=mixer(heads=2, kv=2, dim=10, vdim=6, size=11), mlp={"kind": "dense", "ff": 13}, weights_of=1)],
+                     width=50, vocab=33, taps=5),
     "notaps": config([dict(mixer=mixer(size=4), mlp={"kind": "dense", "ff": 16})], width=32, taps=1),
 }
 
@@ -329,7 +334,7 @@ def test_whole_prompt_matches_the_plain_implementation(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("name", ["mixed", "odd", "taps4"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "taps4", "ragged"])
 def test_decoding_and_portions_equal_the_whole_prompt(name, dtype):
     """Token by token from the first token on; a prompt then 40 single tokens; portions of 2, 3, 1, 7, ... tokens; a step
     longer than the model's step size (cut inside the step function)."""
