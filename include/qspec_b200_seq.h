@@ -60,10 +60,13 @@ int qspec_seq_qk_norm(void* qkv, int ld, const float* q_w, const float* k_w, int
  * weight = sigmoid(cap(score) + bias[h]), cap(s) = softcap * tanh(s / softcap) (softcap <= 0: none),
  * score = scale * q.k; weights are not normalised. Keys at positions inside the token's segment are read from the
  * projection buffer (already normalised), earlier ones from the cache: cache_k [slots, size, G, D],
- * cache_v [slots, size, G, DV], row = position % size. out [ntok, H*DV]. */
+ * cache_v [slots, size, G, DV], row = position % size. out [ntok, H*DV].
+ * max_keys: an upper bound of the keys that any token of the batch sees (its position + 1), 0 if unknown. With few
+ * tokens and many keys each, the key blocks of a token are spread over a thread-block cluster whose CTAs add their
+ * partial sums through distributed shared memory in a fixed order. */
 int qspec_seq_chunk_attention(const void* qkv, int ld, const void* cache_k, const void* cache_v, const float* bias,
                               void* out, const int* meta, int ntok, int H, int G, int D, int DV, int size, float scale,
-                              float softcap, int dtype, void* stream);
+                              float softcap, int max_keys, int dtype, void* stream);
 
 /* Appends the step's keys / values to the cache: only the tokens in the chunk of their segment's LAST token are
  * written (earlier chunks can never be seen again). Runs after qspec_seq_chunk_attention of the same step. */

@@ -114,7 +114,7 @@ SEQ_SIGNATURES = {
                                     c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
     "qspec_seq_qk_norm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "qspec_seq_chunk_attention": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                          c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+                                          c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]),
     "qspec_seq_cache_append": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_int, c_void_p]),
     "qspec_seq_relu2": (c_int, [c_void_p, c_ll, c_int, c_void_p]),

@@ -153,7 +153,8 @@ def _kernel_table(torch, s, hbm_gbs, bf16_tflops):
                                 "(two-term bfloat16 split of the float32 weights) and computes whole 64x64 tiles on the diagonal")
         else:
             us = _time_us(torch, [lambda i=i: ops.seq_chunk_attention(qkv[i % nbuf], ck[i % copies], cv[i % copies], pb, att, tab, H, G, D, D,
-                                                                      size, D ** -0.5, 30.0) for i in range(copies)])
+                                                                      size, D ** -0.5, 30.0, max_keys=max(p for _, p, _ in segs) + 1)
+                                  for i in range(copies)])
             visible = sum((p % size) + 1 for _, p, _ in segs)
             add("seq_chunk_attention (token form)", f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * G * 2 * D * 2)
         hb = [torch.randn(T, W, device=dev).to(bf) for _ in range(nbuf)]

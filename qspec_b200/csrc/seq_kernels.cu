@@ -251,7 +251,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 chunk_attn_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ ck, const T* __restrict__ cv,
                   const float* __restrict__ bias, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H, int G,
-                  int D, int DV, int size, float scale, float softcap) {
+                  int D, int DV, int size, float scale, float softcap, int nsplit) {
   pdl_enter();
   constexpr int WPE = AttWord<T>::N;
   extern __shared__ __align__(16) unsigned char sm_att_raw[];
@@ -294,8 +294,10 @@ chunk_attn_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ ck, c
 #pragma unroll
   for (int k = 0; k < ATT_MAXW; ++k) acc[k][0] = acc[k][1] = 0.f;
   const int nout_w = rep * vw;
-  fetch(0);
-  for (int kb = 0; kb < nkeys; kb += ATT_KB) {
+  // nsplit > 1: the CTAs of a cluster (grid z) take the key blocks in turn and add their partial sums at the end
+  const int kstep = ATT_KB * nsplit, kb0 = ATT_KB * (int)blockIdx.z;
+  if (kb0 < nkeys) fetch(kb0);
+  for (int kb = kb0; kb < nkeys; kb += kstep) {
     __syncthreads();                          // the previous block has been consumed (and q is in place)
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
@@ -308,7 +310,7 @@ chunk_attn_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ ck, c
       }
     }
     __syncthreads();
-    if (kb + ATT_KB < nkeys) fetch(kb + ATT_KB);
+    if (kb + kstep < nkeys) fetch(kb + kstep);
     for (int hh = warp; hh < rep; hh += 4) {
       float w = 0.f;
       if (kb + lane < nkeys) {
@@ -345,11 +347,36 @@ chunk_attn_kernel(const T* __restrict__ qkv, int ld, const T* __restrict__ ck, c
     }
   }
   uint32_t* op = reinterpret_cast<uint32_t*>(out + (size_t)i * H * DV + (size_t)g * rep * DV);
+  if (nsplit == 1) {
+#pragma unroll
+    for (int k = 0; k < ATT_MAXW; ++k) {
+      const int o = tid + k * 128;
+      if (o < nout_w) op[o] = AttWord<T>::put(acc[k][0], acc[k][1]);
+    }
+    return;
+  }
+  // Partial sums of every CTA of the cluster in its own shared memory; CTA r then adds slice r of the output words over
+  // the ranks in rank order (the sum does not depend on which CTA finishes first) and stores it.
+  float* sp = reinterpret_cast<float*>(sv + ATT_KB * vw);     // [nout_w][2]
 #pragma unroll
   for (int k = 0; k < ATT_MAXW; ++k) {
     const int o = tid + k * 128;
-    if (o < nout_w) op[o] = AttWord<T>::put(acc[k][0], acc[k][1]);
+    if (o < nout_w) { sp[2 * o] = acc[k][0]; sp[2 * o + 1] = acc[k][1]; }
   }
+  cluster_sync_all();
+  const int per = (nout_w + nsplit - 1) / nsplit;
+  const int o_end = min(nout_w, ((int)blockIdx.z + 1) * per);
+  const uint32_t sp_addr = (uint32_t)__cvta_generic_to_shared(sp);
+  for (int o = (int)blockIdx.z * per + tid; o < o_end; o += 128) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int r = 0; r < nsplit; ++r) {
+      const uint32_t ra = mapa_shared(sp_addr + 8u * (uint32_t)o, (uint32_t)r);
+      a0 += __uint_as_float(ld_dsmem_u32(ra));
+      if (WPE == 2) a1 += __uint_as_float(ld_dsmem_u32(ra + 4));
+    }
+    op[o] = AttWord<T>::put(a0, a1);
+  }
+  cluster_sync_all();                          // nobody leaves while its partial sums may still be read
 }
 
 // The same for rows that cannot be read as 32-bit words (odd head sizes or leading dimensions in bfloat16): one CTA per
@@ -651,7 +678,7 @@ static int check_attn_args(const void* qkv, int ld, const void* ck, const void* 
 
 extern "C" int qspec_seq_chunk_attention(const void* qkv, int ld, const void* cache_k, const void* cache_v, const float* bias,
                                          void* out, const int* meta, int ntok, int H, int G, int D, int DV, int size, float scale,
-                                         float softcap, int dtype, void* stream) {
+                                         float softcap, int max_keys, int dtype, void* stream) {
   if (int s = check_attn_args(qkv, ld, cache_k, cache_v, meta, ntok, H, G, D, DV, size, "seq_chunk_attention")) return s;
   QSPEC_REQUIRE(bias && out, QSPEC_ERR_INVALID_ARG, "seq_chunk_attention: null pointer");
   SEQ_DTYPE_OK(dtype);
@@ -666,7 +693,15 @@ extern "C" int qspec_seq_chunk_attention(const void* qkv, int ld, const void* ca
                      (((uintptr_t)qkv | (uintptr_t)cache_k | (uintptr_t)cache_v | (uintptr_t)out) & 3) == 0;
   if (words) {
     const int kst = (D / wpe) | 1;
-    const size_t smem = (size_t)(rep * D + rep * ATT_KB) * sizeof(float) + (size_t)ATT_KB * (kst + DV / wpe) * 4;
+    // Few tokens with many keys each (decoding): split the key blocks of a token over a cluster of up to 8 CTAs until
+    // every SM has a few CTAs (measured at 64 tokens x 4 and x 8 key/value heads: 256 -> 512 CTAs 98 -> 55 us, 1024 CTAs
+    // 63 us, 2048 CTAs 78 us -- the kernel is issue-bound, more CTAs than fill the SMs only add their fixed cost).
+    // max_keys bounds the keys any token of the step sees (0: the chunk).
+    const int blocks = ((max_keys > 0 ? min(max_keys, size) : size) + ATT_KB - 1) / ATT_KB;
+    int nsplit = 1;
+    while (nsplit < 8 && nsplit * 2 <= blocks && (long long)ntok * G * nsplit * 2 <= 1024) nsplit *= 2;
+    const size_t smem = (size_t)(rep * D + rep * ATT_KB) * sizeof(float) + (size_t)ATT_KB * (kst + DV / wpe) * 4 +
+                        (nsplit > 1 ? (size_t)rep * (DV / wpe) * 2 * sizeof(float) : 0);
     QSPEC_REQUIRE(smem <= 200 * 1024, QSPEC_ERR_UNSUPPORTED, "seq_chunk_attention: %d query heads of size %d per key/value head do not fit shared memory", rep, D);
     static size_t configured[2] = {0, 0};
     if (smem > 48 * 1024 && smem > configured[w]) {
@@ -674,13 +709,34 @@ extern "C" int qspec_seq_chunk_attention(const void* qkv, int ld, const void* ca
       else QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       configured[w] = smem;
     }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ntok, G, nsplit);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (nsplit > 1) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 1;
+      attr[na].val.clusterDim.y = 1;
+      attr[na].val.clusterDim.z = nsplit;
+      ++na;
+    }
+    if (pdl_enabled()) {
+      attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
     if (w == 0)
-      launch_pdl(chunk_attn_kernel<float>, dim3(ntok, G), dim3(128), smem, st, (const float*)qkv, ld, (const float*)cache_k,
-                 (const float*)cache_v, bias, (float*)out, meta, ntok, H, G, D, DV, size, scale, softcap);
+      QSPEC_CUDA(cudaLaunchKernelEx(&cfg, chunk_attn_kernel<float>, (const float*)qkv, ld, (const float*)cache_k,
+                                    (const float*)cache_v, bias, (float*)out, meta, ntok, H, G, D, DV, size, scale, softcap, nsplit));
     else
-      launch_pdl(chunk_attn_kernel<__nv_bfloat16>, dim3(ntok, G), dim3(128), smem, st, (const __nv_bfloat16*)qkv, ld,
-                 (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, bias, (__nv_bfloat16*)out, meta, ntok, H, G, D, DV,
-                 size, scale, softcap);
+      QSPEC_CUDA(cudaLaunchKernelEx(&cfg, chunk_attn_kernel<__nv_bfloat16>, (const __nv_bfloat16*)qkv, ld,
+                                    (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, bias, (__nv_bfloat16*)out, meta,
+                                    ntok, H, G, D, DV, size, scale, softcap, nsplit));
     QSPEC_CHECK_LAUNCH(1);
     return QSPEC_OK;
   }

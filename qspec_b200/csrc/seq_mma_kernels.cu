@@ -3,6 +3,8 @@
 // mma.sync.m16n8k16 path with float32 accumulators, like this library's other attention kernel for many sequences
 // (seq_attention_kernel): the tiles are short (a chunk of keys; an expert's share of the tokens), and the operands are
 // gathered by row, which is what rules out one large TMA-fed tile per CTA here.
+#include <cstdlib>
+#include <cstring>
 #include "common.cuh"
 #include "../../include/qspec_b200_seq.h"
 
@@ -217,7 +219,7 @@ constexpr size_t GG_SMEM = (size_t)GG_STAGES * 2 * 128 * GG_KP * sizeof(__nv_bfl
 
 struct GroupPlan {
   int* offsets;      // [E + 1] first sorted row of every expert
-  int* cursor;       // [E]
+  int* status;       // [1] status word at the start of the workspace: set to 1 by a CTA whose bounded wait ran out, never cleared
   int* ntiles;       // [1]
   int* tile_expert;  // [max tiles]
   int* tile_row0;    // [max tiles]
@@ -401,6 +403,214 @@ grouped_gemm_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The same product on the fifth-generation tensor cores. One CTA = 128 rows of one expert x 128 B-rows, accumulator
+// [128 lanes x 128 columns] float32 in tensor memory. A and B k-steps of 64 (128 bytes per row) land in shared memory
+// through the same gathering cp.async ring, laid out as the K-major 128-byte-swizzle operand layout (row r at r * 128
+// bytes, 16-byte chunk c at position c ^ (r & 7); 8-row groups 1024 bytes apart), so that one elected thread multiplies a
+// stage with four tcgen05.mma (M 128, N 128, K 16) whose completion (tcgen05.commit on an mbarrier) frees the slot.
+// Every wait is bounded: a barrier that does not complete raises the plan's error word, and the CTA drains its copies,
+// frees its tensor memory and leaves without storing.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int TC_STAGES = 3;                                               // 97 KB: two CTAs per SM
+constexpr int TC_TILE_BYTES = 128 * 128;                                   // 128 rows x 64 bf16
+constexpr size_t TC_SMEM = (size_t)TC_STAGES * 2 * TC_TILE_BYTES + 1024;   // + slack to start on a 1024-byte boundary
+constexpr uint32_t TC_COLS = 128;                                          // tensor-memory columns of the accumulator
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t spins = 0; spins < (1u << 20); ++spins) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ bool tc_elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "elect.sync _|P, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n" : "=r"(pred));
+  return pred != 0;
+}
+// K-major, 128-byte swizzle: start >> 4 at [0,14), stride between 8-row groups (1024 B) >> 4 at [32,46), version 1 at
+// [46,48), layout 2 at [61,64). 32 bytes further along K = + 2 in the start field.
+__device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// float32 accumulator [4,6) = 1, bfloat16 A [7,10) = 1 and B [10,13) = 1, both K-major, N >> 3 at [17,23), M >> 4 at [24,29)
+constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+template <bool DUAL>
+__global__ void __launch_bounds__(256)
+grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, GroupPlan p, int K, int N, int top,
+                       float limit) {
+  pdl_enter();
+  extern __shared__ __align__(16) unsigned char tc_smem_raw[];
+  __shared__ int s_row[GG_BM];
+  __shared__ __align__(8) uint64_t s_bar[TC_STAGES];
+  __shared__ uint32_t s_tmem;
+  __shared__ volatile int s_fail;
+  const int tile = blockIdx.x;
+  if (tile >= *p.ntiles) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t base = (tc_smem_u32(tc_smem_raw) + 1023u) & ~1023u;      // stage s: A at base + s * 32 KB, B 16 KB after it
+  const int e = p.tile_expert[tile], m0 = p.tile_row0[tile];
+  const int mend = p.offsets[e + 1];
+  constexpr int BN = DUAL ? 64 : 128;                    // output columns per CTA
+  const int n0 = blockIdx.y * BN;
+  if (tid < GG_BM) {
+    const int m = m0 + tid;
+    s_row[tid] = m < mend ? p.perm[m] : -1;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) tc_mbar_init(tc_smem_u32(&s_bar[s]), 1);
+    s_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(tc_smem_u32(&s_tmem)), "r"(TC_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem = s_tmem;
+  const bf16* Be = B + (size_t)e * (DUAL ? 2 : 1) * N * K;
+  constexpr int NV = GG_BM * (GG_BK / 8) / 256, VPR = GG_BK / 8;        // 4 vectors of A and 4 of B per thread and stage
+  const bf16* a_src[NV];
+  const bf16* b_src[NV];
+  bool a_ok[NV], b_ok[NV];
+  uint32_t dst[NV];
+#pragma unroll
+  for (int q = 0; q < NV; ++q) {
+    const int v = tid + q * 256, r = v / VPR, c8 = v % VPR;
+    const int pr = s_row[r];
+    a_ok[q] = pr >= 0;
+    a_src[q] = a_ok[q] ? (DUAL ? A + (size_t)(pr / top) * K : A + (size_t)(m0 + r) * K) + c8 * 8 : A;
+    int brow;
+    if (DUAL) brow = (r < 64 ? 0 : N) + n0 + (r & 63);
+    else brow = n0 + r;
+    b_ok[q] = (DUAL ? n0 + (r & 63) : n0 + r) < N;
+    b_src[q] = b_ok[q] ? Be + (size_t)brow * K + c8 * 8 : Be;
+    dst[q] = (uint32_t)(r * 128 + ((c8 ^ (r & 7)) << 4));
+  }
+  auto issue = [&](int stage, int k0) {
+    const uint32_t sa = base + (uint32_t)stage * (2 * TC_TILE_BYTES), sb = sa + TC_TILE_BYTES;
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+      const bool in_k = k0 + (((tid + q * 256) % VPR) * 8) < K;
+      const int na = (a_ok[q] && in_k) ? 16 : 0, nb = (b_ok[q] && in_k) ? 16 : 0;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sa + dst[q]), "l"(a_src[q] + (na ? k0 : 0)), "r"(na) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(sb + dst[q]), "l"(b_src[q] + (nb ? k0 : 0)), "r"(nb) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  const int nk = (K + GG_BK - 1) / GG_BK;
+  // ring: k-step kt lives in slot kt % TC_STAGES; TC_STAGES - 1 steps are in flight while one is multiplied. Past the end
+  // of K the copies are zero-size, so that every iteration commits exactly one group and the wait count stays fixed.
+#pragma unroll
+  for (int s = 0; s < TC_STAGES - 1; ++s) issue(s, s * GG_BK);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int st = kt % TC_STAGES;
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(TC_STAGES - 2) : "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");     // this thread's rows, for the tensor cores' reads
+    __syncthreads();                                                    // k-step kt has landed for everyone
+    if (s_fail) break;                                                  // written before the barrier: uniform
+    if (warp == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      if (tc_elect_one()) {
+        const uint64_t ad = tc_desc_sw128(base + (uint32_t)st * (2 * TC_TILE_BYTES));
+        const uint64_t bd = tc_desc_sw128(base + (uint32_t)st * (2 * TC_TILE_BYTES) + TC_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < GG_BK / 16; ++ks) tc_mma_ss(tmem, ad + 2 * ks, bd + 2 * ks, (kt | ks) ? 1u : 0u);
+        tc_commit(tc_smem_u32(&s_bar[st]));
+      }
+      __syncwarp();
+    }
+    // slot (kt - 1) % TC_STAGES is refilled next: the products of k-step kt - 1 must have read it
+    if (kt >= 1 && !tc_mbar_wait(tc_smem_u32(&s_bar[(kt - 1) % TC_STAGES]), (uint32_t)(((kt - 1) / TC_STAGES) & 1))) s_fail = 1;
+    issue((kt + TC_STAGES - 1) % TC_STAGES, (kt + TC_STAGES - 1) * GG_BK);
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  if (!s_fail && !tc_mbar_wait(tc_smem_u32(&s_bar[(nk - 1) % TC_STAGES]), (uint32_t)(((nk - 1) / TC_STAGES) & 1))) s_fail = 1;
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  if (s_fail) {
+    if (tid == 0) atomicExch(p.status, 1);
+  } else {
+    // warp w reads lanes 32 * (w & 3) .. + 31 (rows of the tile); the two warps of a lane quarter split the columns
+    const int r = (warp & 3) * 32 + lane, half = warp >> 2;
+    const int pr = s_row[r];
+    const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    bf16* crow = DUAL ? C + (size_t)(m0 + r) * N : C + (size_t)(pr < 0 ? 0 : pr) * N;
+    constexpr int GROUPS = DUAL ? 2 : 4;                 // groups of 16 output columns per warp
+#pragma unroll
+    for (int gq = 0; gq < GROUPS; ++gq) {
+      const int col = half * (GROUPS * 16) + gq * 16;    // output column inside the CTA's BN
+      uint32_t a[16], b[16];
+      tc_ld16(trow + (uint32_t)col, a);
+      if (DUAL) tc_ld16(trow + (uint32_t)(64 + col), b);
+      tc_wait_ld();
+      float v[16];
+#pragma unroll
+      for (int x = 0; x < 16; ++x) {
+        if (DUAL) {
+          // projections leave the matrix unit in bfloat16, like the dense layers' products
+          const float gv = fminf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(a[x]))), limit);
+          const float uv = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(b[x]))), -limit), limit);
+          v[x] = gv * (1.0f / (1.0f + expf(-1.702f * gv))) * (uv + 1.0f);
+        } else {
+          v[x] = __uint_as_float(a[x]);
+        }
+      }
+      const int n = n0 + col;
+      if (pr >= 0) {
+        if (n + 16 <= N) {
+          uint4 w0, w1;
+          w0.x = pack_bf2(v[0], v[1]); w0.y = pack_bf2(v[2], v[3]); w0.z = pack_bf2(v[4], v[5]); w0.w = pack_bf2(v[6], v[7]);
+          w1.x = pack_bf2(v[8], v[9]); w1.y = pack_bf2(v[10], v[11]); w1.z = pack_bf2(v[12], v[13]); w1.w = pack_bf2(v[14], v[15]);
+          *reinterpret_cast<uint4*>(crow + n) = w0;
+          *reinterpret_cast<uint4*>(crow + n + 8) = w1;
+        } else {
+#pragma unroll
+          for (int x = 0; x < 16; ++x)
+            if (n + x < N) crow[n + x] = __float2bfloat16_rn(v[x]);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TC_COLS) : "memory");
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace qspec
@@ -433,8 +643,8 @@ extern "C" int qspec_moe_expert_grouped_supported(int W, int F) { return W > 0 &
 static size_t grouped_layout(int ntok, int top, int E, int F, size_t* off) {
   const size_t npairs = (size_t)ntok * top, max_tiles = npairs / 128 + E + 1;
   size_t at = 0;
+  off[1] = at; at = align_up(at + 4, 16);                        // status word (first, wherever the rest lies)
   off[0] = at; at = align_up(at + (size_t)(E + 1) * 4, 16);      // offsets
-  off[1] = at; at = align_up(at + (size_t)(E + 1) * 4, 16);      // cursor (unused slot kept for alignment of the plan)
   off[2] = at; at = align_up(at + 4, 16);                        // ntiles
   off[3] = at; at = align_up(at + max_tiles * 4, 16);            // tile_expert
   off[4] = at; at = align_up(at + max_tiles * 4, 16);            // tile_row0
@@ -463,7 +673,7 @@ extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, cons
   cudaStream_t st = (cudaStream_t)stream;
   unsigned char* ws = (unsigned char*)workspace;
   GroupPlan p;
-  p.offsets = (int*)(ws + off[0]); p.cursor = (int*)(ws + off[1]); p.ntiles = (int*)(ws + off[2]);
+  p.offsets = (int*)(ws + off[0]); p.status = (int*)(ws + off[1]); p.ntiles = (int*)(ws + off[2]);
   p.tile_expert = (int*)(ws + off[3]); p.tile_row0 = (int*)(ws + off[4]); p.perm = (int*)(ws + off[5]);
   bf16* Y = (bf16*)(ws + off[6]);
   const int npairs = ntok * top;
@@ -477,7 +687,20 @@ extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, cons
   if (!configured) {
     QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
     QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
+    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
     configured = true;
+  }
+  // QSPEC_SEQ_GROUPED=mma selects the warp-level (mma.sync) tiles, kept as the comparison form for timing and tests
+  static const bool warp_level = [] { const char* v = getenv("QSPEC_SEQ_GROUPED"); return v && !strcmp(v, "mma"); }();
+  if (!warp_level) {
+    launch_pdl(grouped_gemm_tc_kernel<true>, dim3(max_tiles, (F + 63) / 64), dim3(256), TC_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y,
+               p, W, F, top, limit);
+    QSPEC_CHECK_LAUNCH(1);
+    launch_pdl(grouped_gemm_tc_kernel<false>, dim3(max_tiles, (W + 127) / 128), dim3(256), TC_SMEM, st, (const bf16*)Y, (const bf16*)down,
+               (bf16*)out, p, F, W, top, limit);
+    QSPEC_CHECK_LAUNCH(1);
+    return QSPEC_OK;
   }
   launch_pdl(grouped_gemm_kernel<true>, dim3(max_tiles, (F + 63) / 64), dim3(256), GG_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y, p, W,
              F, top, limit);

@@ -298,6 +298,7 @@ class MutusunModel(torch.nn.Module):
         ya, yb = self.buf_y[0][:T * W].view(T, W), self.buf_y[1][:T * W].view(T, W)
         ops.seq_embed(self.embed, input_ids, xa)
         prompt_shaped = self.use_tiles and T >= self.tiles_min_tokens and T >= 16 * len(meta.segments)
+        max_keys = meta.max_length
         pend = None                                    # (y, part weights, post-norm weight) of the sublayer still to be added
 
         def enter(pre_w, conv_w, tail, out):
@@ -318,7 +319,7 @@ class MutusunModel(torch.nn.Module):
             torch.matmul(h, p.qkv.t(), out=qkv)
             ops.seq_qk_norm(qkv, p.q_norm, p.k_norm, m.heads, m.kv_heads, m.dim, eps)
             ops.seq_chunk_attention(qkv, self.cache_k[i], self.cache_v[i], p.pb, att, tab, m.heads, m.kv_heads, m.dim, m.vdim,
-                                    m.chunk, m.scale, m.softcap,
+                                    m.chunk, m.scale, m.softcap, max_keys=max_keys,
                                     tiles=prompt_shaped and ops.seq_chunk_attention_tiles_supported(qkv, m.heads, m.kv_heads, m.dim, m.vdim))
             ops.seq_cache_append(qkv, self.cache_k[i], self.cache_v[i], tab, m.heads, m.kv_heads, m.dim, m.vdim, m.chunk)
             torch.matmul(att, p.o.t(), out=ya)

@@ -816,9 +816,11 @@ def seq_chunk_attention_tiles_supported(qkv: torch.Tensor, H: int, G: int, D: in
 
 def seq_chunk_attention(qkv: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, bias: torch.Tensor, out: torch.Tensor,
                         meta: torch.Tensor, H: int, G: int, D: int, DV: int, size: int, scale: float, softcap: float,
-                        tiles: bool = False) -> None:
+                        tiles: bool = False, max_keys: int = 0) -> None:
     """Chunk-local sigmoid attention of a token batch; cache_k [slots, size, G, D], cache_v [slots, size, G, DV].
-    tiles=True: the tensor-core form over 64-query tiles (prompt-shaped batches; `seq_chunk_attention_tiles_supported`)."""
+    tiles=True: the tensor-core form over 64-query tiles (prompt-shaped batches; `seq_chunk_attention_tiles_supported`).
+    max_keys: the most keys a token of the batch can see (largest position + 1; 0: unknown) -- the token form spreads the
+    keys of a token over a cluster of CTAs when the batch has few tokens with many keys each."""
     for t, n in ((qkv, "qkv"), (cache_k, "cache_k"), (cache_v, "cache_v"), (out, "out")):
         _chk(t, n, (qkv.dtype,))
     _chk(qkv, "qkv", _SEQ_ACT); _chk(bias, "bias", (_F32,)); _chk(meta, "meta", (torch.int32,))
@@ -832,7 +834,7 @@ def seq_chunk_attention(qkv: torch.Tensor, cache_k: torch.Tensor, cache_v: torch
         return
     _seq(_lib.load_seq().qspec_seq_chunk_attention(_ptr(qkv), qkv.shape[1], _ptr(cache_k), _ptr(cache_v), _ptr(bias), _ptr(out),
                                                    _ptr(meta), ntok, H, G, D, DV, size, float(scale), float(softcap or 0.0),
-                                                   _sdt(qkv), _stream()), "seq_chunk_attention")
+                                                   int(max_keys), _sdt(qkv), _stream()), "seq_chunk_attention")
 
 
 def seq_cache_append(qkv: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, meta: torch.Tensor, H: int, G: int, D: int,
@@ -872,6 +874,14 @@ def moe_expert_tokens(h: torch.Tensor, gate_up: Optional[torch.Tensor], down: Op
         raise ValueError("moe_expert_tokens: shapes do not match")
     _seq(_lib.load_seq().qspec_moe_expert_tokens(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top,
                                                  float(limit), _sdt(h), _stream()), "moe_expert_tokens")
+
+
+def moe_grouped_status(device="cuda") -> int:
+    """0, or 1 once a CTA of the grouped expert products gave up a bounded wait on its pipeline (its rows were not
+    written). Reads the first word of the workspace: synchronises the device."""
+    device = torch.device(device)
+    ws = _workspaces.get(("moe_grouped", device.index if device.index is not None else torch.cuda.current_device()))
+    return 0 if ws is None else int(ws[:4].view(torch.int32).item())
 
 
 def moe_expert_grouped_supported(h: torch.Tensor, F: int) -> bool:

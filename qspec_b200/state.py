@@ -55,6 +55,11 @@ class BatchMeta:
     segments: List[Tuple[Hashable, int, int, int]]     # (request id, slot, first position, token count)
 
     @property
+    def max_length(self) -> int:
+        """Length of the longest sequence once the step has run: no token of the step sees more keys than this."""
+        return max((first + n for _, _, first, n in self.segments), default=0)
+
+    @property
     def slot(self) -> torch.Tensor:
         return self.table[0]
 

@@ -172,6 +172,62 @@ def test_chunk_attention_cache_and_edges(dtype, H, G, D, DV, size, cap):
         close(torch.cat(got[slot]), seqs[slot][1], dtype)
 
 
+def _attention_reference_dense(q, k, v, bias, H, G, size, scale, cap):
+    """The same sum written with whole matrices (float64), for chunks of a few hundred keys."""
+    T = q.shape[0]
+    pos = torch.arange(T)
+    seen = (pos[None, :] <= pos[:, None]) & ((pos[None, :] // size) == (pos[:, None] // size))
+    out = torch.zeros(T, H, v.shape[2], dtype=torch.float64)
+    for h in range(H):
+        g = h // (H // G)
+        s = (q[:, h] @ k[:, g].T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        out[:, h] = (torch.sigmoid(s + bias[h]) * seen) @ v[:, g]
+    return out.reshape(T, -1)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("H,G,D,DV,size", [(4, 2, 16, 8, 70), (8, 2, 32, 64, 300), (3, 1, 64, 32, 129), (2, 2, 128, 128, 257)])
+def test_decoding_attention_with_the_keys_of_a_token_spread_over_a_cluster(dtype, H, G, D, DV, size):
+    """Few tokens, many keys: 2, 4 or 8 CTAs share the key blocks of a token. Two sequences decode across a chunk border
+    (from nearly `size` keys down to one), one of them two positions ahead of the other; the key bound is given or left out."""
+    _cuda()
+    from qspec_b200 import ops
+    g = torch.Generator().manual_seed(size)
+    T = size + 9
+    ld = H * D + G * D + G * DV
+    bias = torch.linspace(-3, -1, H)
+    seqs = {}
+    for slot in (0, 1):
+        qkv = (0.5 * torch.randn(T, ld, generator=g)).to(dtype)
+        f = qkv.to(torch.float64)
+        seqs[slot] = (qkv, _attention_reference_dense(f[:, :H * D].view(T, H, D), f[:, H * D:(H + G) * D].view(T, G, D),
+                                                      f[:, (H + G) * D:].view(T, G, DV), bias.double(), H, G, size, 0.3, 4.0))
+    ck = torch.full((2, size, G, D), 1e4, dtype=dtype, device="cuda")
+    cv = torch.full((2, size, G, DV), 1e4, dtype=dtype, device="cuda")
+    first = {0: size - 7, 1: size - 5}                       # prompt lengths; then one token per step
+    got = {0: [], 1: []}
+    at = dict(first)
+    tab = meta_table([(0, 0, first[0], 0), (1, 0, first[1], 0)])
+    batch = torch.cat((seqs[0][0][:first[0]], seqs[1][0][:first[1]])).cuda()
+    out = torch.empty(batch.shape[0], H * DV, dtype=dtype, device="cuda")
+    ops.seq_chunk_attention(batch, ck, cv, bias.cuda(), out, tab, H, G, D, DV, size, 0.3, 4.0, max_keys=max(first.values()))
+    ops.seq_cache_append(batch, ck, cv, tab, H, G, D, DV, size)
+    got[0].append(out[:first[0]].float().cpu()); got[1].append(out[first[0]:].float().cpu())
+    for step in range(12):
+        tab = meta_table([(1, at[1], 1, 0), (0, at[0], 1, 0)])
+        batch = torch.cat((seqs[1][0][at[1]:at[1] + 1], seqs[0][0][at[0]:at[0] + 1])).cuda()
+        out = torch.empty(2, H * DV, dtype=dtype, device="cuda")
+        ops.seq_chunk_attention(batch, ck, cv, bias.cuda(), out, tab, H, G, D, DV, size, 0.3, 4.0,
+                                max_keys=(at[1] + 1) if step % 2 else 0)
+        ops.seq_cache_append(batch, ck, cv, tab, H, G, D, DV, size)
+        got[1].append(out[:1].float().cpu()); got[0].append(out[1:].float().cpu())
+        at[0] += 1; at[1] += 1
+    for slot in (0, 1):
+        close(torch.cat(got[slot]), seqs[slot][1][:at[slot]], dtype)
+
+
 def test_attention_far_key_inside_and_outside_the_chunk():
     """One key is made to dominate (score pushed up, bias keeps all others near zero weight): the output equals that key's
     value exactly when it lies in the query's chunk -- first row of the chunk included -- and not one row further."""
@@ -490,6 +546,7 @@ def test_grouped_experts_equal_the_token_form(W, F, E, ident, top):
     scale = float(a.float().abs().max())
     assert float((a.float() - b.float()).abs().max()) <= 2e-2 * scale
     assert float((a.float() - b.float()).abs().mean()) <= 2e-3 * scale
+    assert ops.moe_grouped_status() == 0                    # no CTA gave up a wait of its pipeline
 
 
 CONFIGS["tiles"] = config([dict(mixer=mixer(heads=2, kv=1, dim=64, vdim=64, size=40), mlp=moe(ff=32, experts=4, identity=2, top=2)),
