@@ -2,10 +2,17 @@
 // short causal convolution over time, per-head query/key norms, chunk-local sigmoid attention over a per-slot cache,
 // router and expert feed-forward in the token-per-CTA form. Templated on the element type of activations and large
 // weights (bfloat16 / float32); every reduction, exponential and the residual stream are float32 in both.
+#include <cstdlib>
+#include <cstring>
 #include "common.cuh"
 #include "../../include/qspec_b200_seq.h"
 
 namespace qspec {
+
+// seq_mma_kernels.cu: the token form on the tensor cores; -1 if it does not take the shape
+int chunk_attention_token_mma(const void* qkv, int ld, const void* ck, const void* cv, const float* bias, void* out, const int* meta,
+                              int ntok, int H, int G, int D, int DV, int size, float scale, float softcap, int max_keys,
+                              cudaStream_t st);
 
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -684,6 +691,13 @@ extern "C" int qspec_seq_chunk_attention(const void* qkv, int ld, const void* ca
   SEQ_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
   const int rep = H / G;
+  // bfloat16 rows of head sizes 64 / 128: the tensor-core form (seq_mma_kernels.cu); QSPEC_SEQ_ATT=scalar keeps this file's
+  static const bool scalar_only = [] { const char* v = getenv("QSPEC_SEQ_ATT"); return v && !strcmp(v, "scalar"); }();
+  if (dtype == QSPEC_DTYPE_BF16 && !scalar_only) {
+    const int s = chunk_attention_token_mma(qkv, ld, cache_k, cache_v, bias, out, meta, ntok, H, G, D, DV, size, scale, softcap,
+                                            max_keys, (cudaStream_t)stream);
+    if (s >= 0) return s;
+  }
   const int wpe = dtype == QSPEC_DTYPE_F32 ? 1 : 2;
   const int w = dtype == QSPEC_DTYPE_F32 ? 0 : 1;
   cudaStream_t st = (cudaStream_t)stream;

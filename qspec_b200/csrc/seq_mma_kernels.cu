@@ -1,8 +1,10 @@
-// Tensor-core forms of the sequence-mixer kernels for many tokens per step (bfloat16 only; include/qspec_b200_seq.h):
-// chunk-local sigmoid attention over 64-query tiles and the grouped expert feed-forward. Both use the warp-level
-// mma.sync.m16n8k16 path with float32 accumulators, like this library's other attention kernel for many sequences
-// (seq_attention_kernel): the tiles are short (a chunk of keys; an expert's share of the tokens), and the operands are
-// gathered by row, which is what rules out one large TMA-fed tile per CTA here.
+// Tensor-core forms of the sequence-mixer kernels (bfloat16 only; include/qspec_b200_seq.h):
+//  * chunk-local sigmoid attention over 64-query tiles (prompts) and per token (decoding): warp-level mma.sync.m16n8k16
+//    with float32 accumulators, like this library's other attention kernel for many sequences (seq_attention_kernel) --
+//    the products are short (a chunk of keys, a handful of query heads) and their rows are gathered from two places;
+//  * the grouped expert feed-forward: tcgen05.mma with the accumulator in tensor memory, operands gathered row by row
+//    into the swizzled shared-memory operand layout by cp.async (the rows of an expert are scattered over the batch,
+//    which is what rules out a plain TMA tile). The warp-level form of the same product is kept for comparison.
 #include <cstdlib>
 #include <cstring>
 #include "common.cuh"
@@ -28,6 +30,16 @@ __device__ __forceinline__ void split_bf2(float w0, float w1, uint32_t& hi, uint
   hv.x = h0; hv.y = h1;
   hi = *reinterpret_cast<uint32_t*>(&hv);
   lo = pack_bf2(w0 - __bfloat162float(h0), w1 - __bfloat162float(h1));
+}
+
+// Weight of a visible key in the bfloat16 kernels: float32 throughout, with the exponentials on the special-function unit
+// (ex2.approx: two units in the last place) instead of the exact library routines, which cost ~80 instructions a weight.
+// tanh(u) = 1 - 2 / (e^(2u) + 1): its absolute error (~1e-7) is what the capped score carries into the sigmoid; the
+// operands q and k are bfloat16 roundings (relative 4e-3), so nothing of this shows. Limits: e -> inf gives 1, e -> 0 gives -1.
+__device__ __forceinline__ float capped_sigmoid_fast(float dot, float scale, float softcap, float bias) {
+  float s = dot * scale;
+  if (softcap > 0.f) s = softcap * (1.0f - __fdividef(2.0f, __expf(2.0f * s / softcap) + 1.0f));
+  return __fdividef(1.0f, 1.0f + __expf(-(s + bias)));
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -163,9 +175,7 @@ chunk_attn_mma_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restri
         for (int e = 0; e < 4; ++e) {
           const int j = kb + nt * 8 + tig * 2 + (e & 1);
           const bool vis = e < 2 ? (okA && j >= loA && j <= hiA) : (okB && j >= loB && j <= hiB);
-          float s = sacc[nt][e] * scale;
-          if (softcap > 0.f) s = softcap * tanhf(s / softcap);
-          sacc[nt][e] = vis ? 1.0f / (1.0f + expf(-(s + b))) : 0.f;
+          sacc[nt][e] = vis ? capped_sigmoid_fast(sacc[nt][e], scale, softcap, b) : 0.f;
         }
       }
 #pragma unroll
@@ -206,6 +216,211 @@ static int launch_attn_mma(const void* qkv, int ld, const void* ck, const void* 
              (const bf16*)cv, bias, (bf16*)out, meta, ntok, H, G, size, scale, softcap);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Attention for decode-shaped batches on the tensor cores. One CTA (4 warps) per (token, key/value head), optionally a
+// cluster of CTAs per token; the rows of every product are the H/G query heads that share the key/value head (up to 16).
+// A warp takes whole blocks of 32 keys: K and V rows go from global memory straight into the mma.sync fragments with
+// 16-byte loads -- no shared memory, no transposes -- because both sums are free in the order of their terms:
+//  * q.k: the 8 consecutive elements a thread loads of key n (d = 32 j + 8 tig + 0..7) serve as the B fragments of two
+//    k-steps; the query fragments are read from shared memory through the same permutation of d;
+//  * weights.v: a thread loads, for its four keys of a k-step, elements d = 64 s + 8 gid + 0..7; element t of the four
+//    vectors forms the B fragment of output tile t, whose column `gid` therefore stands for d = 64 s + 8 gid + t.
+// Weights are float32 and enter the second product as a two-term bfloat16 split. Partial sums of the warps are added
+// through shared memory, those of the cluster's CTAs through distributed shared memory, both in a fixed order.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int D, int DV>
+__global__ void __launch_bounds__(128, 2)
+chunk_attn_token_mma_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __restrict__ ck, const bf16* __restrict__ cv,
+                            const float* __restrict__ bias, bf16* __restrict__ out, const int* __restrict__ meta, int ntok, int H,
+                            int G, int size, float scale, float softcap, int nsplit) {
+  pdl_enter();
+  constexpr int QS = D / 2 + 4;                           // words per query row in shared memory
+  extern __shared__ __align__(16) unsigned char tk_raw[];
+  const int rep = H / G;
+  uint32_t* sQ = reinterpret_cast<uint32_t*>(tk_raw);     // [16][QS], rows >= rep zero
+  float* sO = reinterpret_cast<float*>(sQ + 16 * QS);     // [4 warps][rep][DV]
+  float* sP = sO + 4 * rep * DV;                          // [rep][DV]: this CTA's partial sums (clusters only)
+  const int i = blockIdx.x, g = blockIdx.y, rank = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int slot = meta[i], pos = meta[ntok + i], sb = meta[2 * ntok + i];
+  const int pos_start = pos - (i - sb);
+  const int lo = (pos / size) * size;
+  const int nkeys = pos - lo + 1;
+  const int koff = H * D + g * D, voff = H * D + G * D + g * DV;
+  for (int c = tid; c < 16 * (D / 2); c += 128) {
+    const int row = c / (D / 2), w = c - row * (D / 2);
+    sQ[row * QS + w] = row < rep ? reinterpret_cast<const uint32_t*>(qkv + (size_t)i * ld + (size_t)(g * rep + row) * D)[w] : 0u;
+  }
+  __syncthreads();
+  const float bias0 = gid < rep ? bias[g * rep + gid] : 0.f, bias1 = gid + 8 < rep ? bias[g * rep + gid + 8] : 0.f;
+  float o[DV / 8][4];
+#pragma unroll
+  for (int t = 0; t < DV / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  for (int blk = rank * 4 + warp; blk * 32 < nkeys; blk += 4 * nsplit) {
+    const int kb = blk * 32;
+    uint4 kr[4][D / 32];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int jj = kb + 8 * nt + gid;
+      const bool ok = jj < nkeys;
+      const int pj = lo + jj;
+      const bf16* kp = (ok && pj >= pos_start) ? qkv + (size_t)(sb + pj - pos_start) * ld + koff
+                                               : ck + (((size_t)slot * size + (ok ? jj : 0)) * G + g) * D;
+#pragma unroll
+      for (int j = 0; j < D / 32; ++j) kr[nt][j] = ok ? __ldg(reinterpret_cast<const uint4*>(kp + 32 * j + 8 * tig)) : zero4;
+    }
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int j = 0; j < D / 32; ++j)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int wq = 16 * j + 4 * tig + 2 * half;
+        const uint32_t a[4] = {sQ[gid * QS + wq], sQ[(gid + 8) * QS + wq], sQ[gid * QS + wq + 1], sQ[(gid + 8) * QS + wq + 1]};
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+          mma_bf16_16816(s[nt], a, half ? kr[nt][j].z : kr[nt][j].x, half ? kr[nt][j].w : kr[nt][j].y);
+      }
+    // values of this block: k-step kk covers keys kb + 16 kk + {2 tig, 2 tig + 1, 8 + 2 tig, 9 + 2 tig}
+    uint4 vr[2][4][DV / 64];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int jj = kb + 16 * kk + 2 * tig + (q & 1) + 8 * (q >> 1);
+        const bool ok = jj < nkeys;
+        const int pj = lo + jj;
+        const bf16* vp = (ok && pj >= pos_start) ? qkv + (size_t)(sb + pj - pos_start) * ld + voff
+                                                 : cv + (((size_t)slot * size + (ok ? jj : 0)) * G + g) * DV;
+#pragma unroll
+        for (int sp = 0; sp < DV / 64; ++sp) vr[kk][q][sp] = ok ? __ldg(reinterpret_cast<const uint4*>(vp + 64 * sp + 8 * gid)) : zero4;
+      }
+    float w[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int row = gid + 8 * (c >> 1), key = kb + 8 * nt + 2 * tig + (c & 1);
+        w[nt][c] = (row < rep && key < nkeys) ? capped_sigmoid_fast(s[nt][c], scale, softcap, (c >> 1) ? bias1 : bias0) : 0.f;
+      }
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      uint32_t ah[4], al[4];
+      split_bf2(w[2 * kk][0], w[2 * kk][1], ah[0], al[0]);
+      split_bf2(w[2 * kk][2], w[2 * kk][3], ah[1], al[1]);
+      split_bf2(w[2 * kk + 1][0], w[2 * kk + 1][1], ah[2], al[2]);
+      split_bf2(w[2 * kk + 1][2], w[2 * kk + 1][3], ah[3], al[3]);
+#pragma unroll
+      for (int sp = 0; sp < DV / 64; ++sp) {
+        const uint32_t v0[4] = {vr[kk][0][sp].x, vr[kk][0][sp].y, vr[kk][0][sp].z, vr[kk][0][sp].w};
+        const uint32_t v1[4] = {vr[kk][1][sp].x, vr[kk][1][sp].y, vr[kk][1][sp].z, vr[kk][1][sp].w};
+        const uint32_t v2[4] = {vr[kk][2][sp].x, vr[kk][2][sp].y, vr[kk][2][sp].z, vr[kk][2][sp].w};
+        const uint32_t v3[4] = {vr[kk][3][sp].x, vr[kk][3][sp].y, vr[kk][3][sp].z, vr[kk][3][sp].w};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const uint32_t sel = (t & 1) ? 0x7632u : 0x5410u;
+          const uint32_t b0 = __byte_perm(v0[t >> 1], v1[t >> 1], sel), b1 = __byte_perm(v2[t >> 1], v3[t >> 1], sel);
+          mma_bf16_16816(o[sp * 8 + t], ah, b0, b1);
+          mma_bf16_16816(o[sp * 8 + t], al, b0, b1);
+        }
+      }
+    }
+  }
+  // this warp's sums: tile (sp, t), register c -> row gid + 8 (c >> 1), d = 64 sp + 8 (2 tig + (c & 1)) + t
+#pragma unroll
+  for (int sp = 0; sp < DV / 64; ++sp)
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int row = gid + 8 * (c >> 1);
+        if (row < rep) sO[(warp * rep + row) * DV + 64 * sp + 8 * (2 * tig + (c & 1)) + t] = o[sp * 8 + t][c];
+      }
+  __syncthreads();
+  const int nout = rep * DV;
+  uint32_t* op = reinterpret_cast<uint32_t*>(out + (size_t)i * H * DV + (size_t)g * rep * DV);
+  for (int e = 2 * tid; e < nout; e += 256) {
+    const float a0 = ((sO[e] + sO[nout + e]) + sO[2 * nout + e]) + sO[3 * nout + e];
+    const float a1 = ((sO[e + 1] + sO[nout + e + 1]) + sO[2 * nout + e + 1]) + sO[3 * nout + e + 1];
+    if (nsplit == 1) op[e >> 1] = pack_bf2(a0, a1);
+    else { sP[e] = a0; sP[e + 1] = a1; }
+  }
+  if (nsplit == 1) return;
+  cluster_sync_all();
+  const int words = nout >> 1, per = (words + nsplit - 1) / nsplit;
+  const int w_end = min(words, (rank + 1) * per);
+  const uint32_t sp_addr = (uint32_t)__cvta_generic_to_shared(sP);
+  for (int wd = rank * per + tid; wd < w_end; wd += 128) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int r = 0; r < nsplit; ++r) {
+      const uint32_t ra = mapa_shared(sp_addr + 8u * (uint32_t)wd, (uint32_t)r);
+      a0 += __uint_as_float(ld_dsmem_u32(ra));
+      a1 += __uint_as_float(ld_dsmem_u32(ra + 4));
+    }
+    op[wd] = pack_bf2(a0, a1);
+  }
+  cluster_sync_all();                          // nobody leaves while its partial sums may still be read
+}
+
+template <int D, int DV>
+static int launch_attn_token_mma(const void* qkv, int ld, const void* ck, const void* cv, const float* bias, void* out, const int* meta,
+                                 int ntok, int H, int G, int size, float scale, float softcap, int max_keys, cudaStream_t st) {
+  const int rep = H / G;
+  const int blocks = ((max_keys > 0 ? min(max_keys, size) : size) + 31) / 32;
+  // A cluster per token only while the grid would otherwise leave SMs empty: at 256 and 512 CTAs (64 tokens x 4 and 8
+  // key/value heads, 544 and 1056 keys) every doubling of the CTAs made the kernel slower (32 / 42 / 58 / 82 us and
+  // 105 / 125 / 157 / 233 us for 1 / 2 / 4 / 8 CTAs per token) -- the fixed chain of a CTA (table, queries, first keys,
+  // the sums at the end) is what a short kernel pays for, not the blocks of one warp.
+  int nsplit = 1;
+  while (nsplit < 8 && 4 * nsplit < blocks && (long long)ntok * G * nsplit * 2 <= 296) nsplit *= 2;
+  const size_t smem = (size_t)16 * (D / 2 + 4) * 4 + (size_t)(4 + (nsplit > 1 ? 1 : 0)) * rep * DV * sizeof(float);
+  static size_t configured = 0;                          // per instantiation
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(chunk_attn_token_mma_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ntok, G, nsplit);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (nsplit > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = nsplit;
+    ++na;
+  }
+  if (pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  QSPEC_CUDA(cudaLaunchKernelEx(&cfg, chunk_attn_token_mma_kernel<D, DV>, (const bf16*)qkv, ld, (const bf16*)ck, (const bf16*)cv, bias,
+                                (bf16*)out, meta, ntok, H, G, size, scale, softcap, nsplit));
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+// Entry for qspec_seq_chunk_attention (seq_kernels.cu): returns -1 when the shape is not one this form takes.
+int chunk_attention_token_mma(const void* qkv, int ld, const void* ck, const void* cv, const float* bias, void* out, const int* meta,
+                              int ntok, int H, int G, int D, int DV, int size, float scale, float softcap, int max_keys,
+                              cudaStream_t st) {
+  const bool ok = H % G == 0 && H / G <= 16 && (D == 64 || D == 128) && (DV == 64 || DV == 128) && ld % 8 == 0 &&
+                  (((uintptr_t)qkv | (uintptr_t)ck | (uintptr_t)cv | (uintptr_t)out) & 15) == 0;
+  if (!ok) return -1;
+  if (D == 64 && DV == 64) return launch_attn_token_mma<64, 64>(qkv, ld, ck, cv, bias, out, meta, ntok, H, G, size, scale, softcap, max_keys, st);
+  if (D == 64) return launch_attn_token_mma<64, 128>(qkv, ld, ck, cv, bias, out, meta, ntok, H, G, size, scale, softcap, max_keys, st);
+  if (DV == 64) return launch_attn_token_mma<128, 64>(qkv, ld, ck, cv, bias, out, meta, ntok, H, G, size, scale, softcap, max_keys, st);
+  return launch_attn_token_mma<128, 128>(qkv, ld, ck, cv, bias, out, meta, ntok, H, G, size, scale, softcap, max_keys, st);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

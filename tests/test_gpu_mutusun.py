@@ -188,10 +188,14 @@ def _attention_reference_dense(q, k, v, bias, H, G, size, scale, cap):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("H,G,D,DV,size", [(4, 2, 16, 8, 70), (8, 2, 32, 64, 300), (3, 1, 64, 32, 129), (2, 2, 128, 128, 257)])
+@pytest.mark.parametrize("H,G,D,DV,size", [(4, 2, 16, 8, 70), (8, 2, 32, 64, 300), (3, 1, 64, 32, 129), (2, 2, 128, 128, 257),
+                                           (8, 2, 64, 64, 300), (12, 2, 128, 64, 100), (16, 1, 64, 128, 70), (12, 1, 128, 128, 33),
+                                           (1, 1, 64, 64, 31)])
 def test_decoding_attention_with_the_keys_of_a_token_spread_over_a_cluster(dtype, H, G, D, DV, size):
     """Few tokens, many keys: 2, 4 or 8 CTAs share the key blocks of a token. Two sequences decode across a chunk border
-    (from nearly `size` keys down to one), one of them two positions ahead of the other; the key bound is given or left out."""
+    (from nearly `size` keys down to one), one of them two positions ahead of the other; the key bound is given or left out.
+    Head sizes of 64 / 128 in bfloat16 take the tensor-core token form (1 to 16 query heads per key/value head, more
+    than 8 included), the others and float32 the element-wise one."""
     _cuda()
     from qspec_b200 import ops
     g = torch.Generator().manual_seed(size)
