@@ -161,6 +161,15 @@ def load_seq() -> ctypes.CDLL:
     global _seq_lib
     if _seq_lib is not None:
         return _seq_lib
+    if not os.environ.get("QSPEC_SEQ_LIB"):
+        # a library older than its sources is rebuilt (20 s) rather than loaded: kernels and bindings must not drift apart
+        from . import build
+        try:
+            build.build_seq_library()
+        except Exception as e:  # no compiler or a read-only tree: an existing library is still the best there is
+            if os.path.exists(SEQ_LIB_PATH):
+                import warnings
+                warnings.warn(f"{SEQ_LIB_PATH} may be older than its sources and could not be rebuilt: {e}")
     if not os.path.exists(SEQ_LIB_PATH):
         raise ImportError(
             f"{SEQ_LIB_PATH} is missing: build it with `python -m qspec_b200.build --seq` "

@@ -394,7 +394,7 @@ def test_whole_prompt_matches_the_plain_implementation(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("name", ["mixed", "odd", "taps4", "ragged"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "taps4", "ragged", "tiles"])
 def test_decoding_and_portions_equal_the_whole_prompt(name, dtype):
     """Token by token from the first token on; a prompt then 40 single tokens; portions of 2, 3, 1, 7, ... tokens; a step
     longer than the model's step size (cut inside the step function)."""
