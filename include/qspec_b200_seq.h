@@ -94,7 +94,10 @@ int qspec_moe_route(const void* h, const float* router_w, const float* correctio
 int qspec_moe_expert_tokens(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
                             int W, int F, int E, int top, float limit, int dtype, void* stream);
 
-/* Grouped form for many tokens (bfloat16, tensor cores). Workspace layout is internal; bytes from the query. */
+/* Grouped form for many tokens (bfloat16): the (token, choice) pairs are sorted by expert and every expert's rows go
+ * through 128 x 128 tcgen05 tiles with the accumulator in tensor memory. Workspace: bytes from the query, zero-filled
+ * once by the caller; its layout is internal except for the first int32, a status word that a CTA sets to 1 when a
+ * bounded wait of its pipeline runs out (that CTA stores nothing); no call clears it. */
 size_t qspec_moe_grouped_workspace_bytes(int ntok, int top, int E, int F);
 int qspec_moe_expert_grouped(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
                              int W, int F, int E, int top, float limit, void* workspace, size_t workspace_bytes,
