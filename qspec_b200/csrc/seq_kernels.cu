@@ -469,10 +469,24 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
   float* ch = sm_rt + R;
   const int i = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T* hp = h + (size_t)i * W;
+  // four elements per lane and load where the rows allow it, four such loads in flight: the dot products are short and
+  // latency-bound (router weights and the token's row both come from the L1 / L2)
+  const bool vec = (W & 3) == 0 && ((uintptr_t)rw & 15) == 0 && ((uintptr_t)hp & (4 * sizeof(T) - 1)) == 0;
   for (int r = warp; r < R; r += 4) {
     const float* wr = rw + (size_t)r * W;
     float acc = 0.f;
-    for (int c = lane; c < W; c += 32) acc += wr[c] * to_f(hp[c]);
+    if (vec) {
+      float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+      for (int c = lane * 4; c < W; c += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(wr + c);
+        const VecF<4> hv = ldv<4>(hp + c);
+        a4[0] += wv.x * hv.v[0]; a4[1] += wv.y * hv.v[1]; a4[2] += wv.z * hv.v[2]; a4[3] += wv.w * hv.v[3];
+      }
+      acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+    } else {
+      for (int c = lane; c < W; c += 32) acc += wr[c] * to_f(hp[c]);
+    }
     acc = warp_xor_sum(acc);
     if (lane == 0) z[r] = acc;
   }

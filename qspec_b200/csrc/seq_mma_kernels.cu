@@ -221,11 +221,12 @@ static int launch_attn_mma(const void* qkv, int ld, const void* ck, const void* 
 // ---------------------------------------------------------------------------------------------------------------------
 // Attention for decode-shaped batches on the tensor cores. One CTA (4 warps) per (token, key/value head), optionally a
 // cluster of CTAs per token; the rows of every product are the H/G query heads that share the key/value head (up to 16).
-// A warp takes whole blocks of 32 keys: K and V rows go from global memory straight into the mma.sync fragments with
-// 16-byte loads -- no shared memory, no transposes -- because both sums are free in the order of their terms:
+// A warp takes steps of 16 keys, the next step's rows in flight while it multiplies the current one: K and V rows go from
+// global memory straight into the mma.sync fragments with 16-byte loads -- no shared memory, no transposes -- because
+// both sums are free in the order of their terms:
 //  * q.k: the 8 consecutive elements a thread loads of key n (d = 32 j + 8 tig + 0..7) serve as the B fragments of two
 //    k-steps; the query fragments are read from shared memory through the same permutation of d;
-//  * weights.v: a thread loads, for its four keys of a k-step, elements d = 64 s + 8 gid + 0..7; element t of the four
+//  * weights.v: a thread loads, for its four keys of a step, elements d = 64 s + 8 gid + 0..7; element t of the four
 //    vectors forms the B fragment of output tile t, whose column `gid` therefore stands for d = 64 s + 8 gid + t.
 // Weights are float32 and enter the second product as a two-term bfloat16 split. Partial sums of the warps are added
 // through shared memory, those of the cluster's CTAs through distributed shared memory, both in a fixed order.
@@ -259,22 +260,43 @@ chunk_attn_token_mma_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __
 #pragma unroll
   for (int t = 0; t < DV / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-  for (int blk = rank * 4 + warp; blk * 32 < nkeys; blk += 4 * nsplit) {
-    const int kb = blk * 32;
-    uint4 kr[4][D / 32];
+  // The warp's steps of 16 keys (step hb covers keys 16 hb ..): the rows of the next step are in flight while the current
+  // one is multiplied. k[nt][j]: key 16 hb + 8 nt + gid, elements 32 j + 8 tig ..; v[q][sp]: key 16 hb + 2 tig + (q & 1) +
+  // 8 (q >> 1), elements 64 sp + 8 gid ..
+  struct Rows { uint4 k[2][D / 32]; uint4 v[4][DV / 64]; };
+  auto fetch = [&](int hb, Rows& r) {
+    const int kb = hb * 16;
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+    for (int nt = 0; nt < 2; ++nt) {
       const int jj = kb + 8 * nt + gid;
       const bool ok = jj < nkeys;
       const int pj = lo + jj;
       const bf16* kp = (ok && pj >= pos_start) ? qkv + (size_t)(sb + pj - pos_start) * ld + koff
                                                : ck + (((size_t)slot * size + (ok ? jj : 0)) * G + g) * D;
 #pragma unroll
-      for (int j = 0; j < D / 32; ++j) kr[nt][j] = ok ? __ldg(reinterpret_cast<const uint4*>(kp + 32 * j + 8 * tig)) : zero4;
+      for (int j = 0; j < D / 32; ++j) r.k[nt][j] = ok ? __ldg(reinterpret_cast<const uint4*>(kp + 32 * j + 8 * tig)) : zero4;
     }
-    float s[4][4];
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    for (int q = 0; q < 4; ++q) {
+      const int jj = kb + 2 * tig + (q & 1) + 8 * (q >> 1);
+      const bool ok = jj < nkeys;
+      const int pj = lo + jj;
+      const bf16* vp = (ok && pj >= pos_start) ? qkv + (size_t)(sb + pj - pos_start) * ld + voff
+                                               : cv + (((size_t)slot * size + (ok ? jj : 0)) * G + g) * DV;
+#pragma unroll
+      for (int sp = 0; sp < DV / 64; ++sp) r.v[q][sp] = ok ? __ldg(reinterpret_cast<const uint4*>(vp + 64 * sp + 8 * gid)) : zero4;
+    }
+  };
+  const int hstep = 4 * nsplit;
+  Rows cur, nxt;
+  int hb = rank * 4 + warp;
+  if (hb * 16 < nkeys) fetch(hb, cur);
+  for (; hb * 16 < nkeys; hb += hstep) {
+    const int kb = hb * 16;
+    if ((hb + hstep) * 16 < nkeys) fetch(hb + hstep, nxt);
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
     for (int j = 0; j < D / 32; ++j)
 #pragma unroll
@@ -282,53 +304,37 @@ chunk_attn_token_mma_kernel(const bf16* __restrict__ qkv, int ld, const bf16* __
         const int wq = 16 * j + 4 * tig + 2 * half;
         const uint32_t a[4] = {sQ[gid * QS + wq], sQ[(gid + 8) * QS + wq], sQ[gid * QS + wq + 1], sQ[(gid + 8) * QS + wq + 1]};
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
-          mma_bf16_16816(s[nt], a, half ? kr[nt][j].z : kr[nt][j].x, half ? kr[nt][j].w : kr[nt][j].y);
+        for (int nt = 0; nt < 2; ++nt)
+          mma_bf16_16816(s[nt], a, half ? cur.k[nt][j].z : cur.k[nt][j].x, half ? cur.k[nt][j].w : cur.k[nt][j].y);
       }
-    // values of this block: k-step kk covers keys kb + 16 kk + {2 tig, 2 tig + 1, 8 + 2 tig, 9 + 2 tig}
-    uint4 vr[2][4][DV / 64];
+    float w[2][4];
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk)
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int jj = kb + 16 * kk + 2 * tig + (q & 1) + 8 * (q >> 1);
-        const bool ok = jj < nkeys;
-        const int pj = lo + jj;
-        const bf16* vp = (ok && pj >= pos_start) ? qkv + (size_t)(sb + pj - pos_start) * ld + voff
-                                                 : cv + (((size_t)slot * size + (ok ? jj : 0)) * G + g) * DV;
-#pragma unroll
-        for (int sp = 0; sp < DV / 64; ++sp) vr[kk][q][sp] = ok ? __ldg(reinterpret_cast<const uint4*>(vp + 64 * sp + 8 * gid)) : zero4;
-      }
-    float w[4][4];
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
+    for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int row = gid + 8 * (c >> 1), key = kb + 8 * nt + 2 * tig + (c & 1);
         w[nt][c] = (row < rep && key < nkeys) ? capped_sigmoid_fast(s[nt][c], scale, softcap, (c >> 1) ? bias1 : bias0) : 0.f;
       }
+    uint32_t ah[4], al[4];
+    split_bf2(w[0][0], w[0][1], ah[0], al[0]);
+    split_bf2(w[0][2], w[0][3], ah[1], al[1]);
+    split_bf2(w[1][0], w[1][1], ah[2], al[2]);
+    split_bf2(w[1][2], w[1][3], ah[3], al[3]);
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
-      uint32_t ah[4], al[4];
-      split_bf2(w[2 * kk][0], w[2 * kk][1], ah[0], al[0]);
-      split_bf2(w[2 * kk][2], w[2 * kk][3], ah[1], al[1]);
-      split_bf2(w[2 * kk + 1][0], w[2 * kk + 1][1], ah[2], al[2]);
-      split_bf2(w[2 * kk + 1][2], w[2 * kk + 1][3], ah[3], al[3]);
+    for (int sp = 0; sp < DV / 64; ++sp) {
+      const uint32_t v0[4] = {cur.v[0][sp].x, cur.v[0][sp].y, cur.v[0][sp].z, cur.v[0][sp].w};
+      const uint32_t v1[4] = {cur.v[1][sp].x, cur.v[1][sp].y, cur.v[1][sp].z, cur.v[1][sp].w};
+      const uint32_t v2[4] = {cur.v[2][sp].x, cur.v[2][sp].y, cur.v[2][sp].z, cur.v[2][sp].w};
+      const uint32_t v3[4] = {cur.v[3][sp].x, cur.v[3][sp].y, cur.v[3][sp].z, cur.v[3][sp].w};
 #pragma unroll
-      for (int sp = 0; sp < DV / 64; ++sp) {
-        const uint32_t v0[4] = {vr[kk][0][sp].x, vr[kk][0][sp].y, vr[kk][0][sp].z, vr[kk][0][sp].w};
-        const uint32_t v1[4] = {vr[kk][1][sp].x, vr[kk][1][sp].y, vr[kk][1][sp].z, vr[kk][1][sp].w};
-        const uint32_t v2[4] = {vr[kk][2][sp].x, vr[kk][2][sp].y, vr[kk][2][sp].z, vr[kk][2][sp].w};
-        const uint32_t v3[4] = {vr[kk][3][sp].x, vr[kk][3][sp].y, vr[kk][3][sp].z, vr[kk][3][sp].w};
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          const uint32_t sel = (t & 1) ? 0x7632u : 0x5410u;
-          const uint32_t b0 = __byte_perm(v0[t >> 1], v1[t >> 1], sel), b1 = __byte_perm(v2[t >> 1], v3[t >> 1], sel);
-          mma_bf16_16816(o[sp * 8 + t], ah, b0, b1);
-          mma_bf16_16816(o[sp * 8 + t], al, b0, b1);
-        }
+      for (int t = 0; t < 8; ++t) {
+        const uint32_t sel = (t & 1) ? 0x7632u : 0x5410u;
+        const uint32_t b0 = __byte_perm(v0[t >> 1], v1[t >> 1], sel), b1 = __byte_perm(v2[t >> 1], v3[t >> 1], sel);
+        mma_bf16_16816(o[sp * 8 + t], ah, b0, b1);
+        mma_bf16_16816(o[sp * 8 + t], al, b0, b1);
       }
     }
+    cur = nxt;
   }
   // this warp's sums: tile (sp, t), register c -> row gid + 8 (c >> 1), d = 64 sp + 8 (2 tig + (c & 1)) + t
 #pragma unroll
