@@ -45,11 +45,13 @@ int qspec_seq_embed(const void* table, const int* ids, float* x, int ntok, int W
  * out == NULL stops after r. tail: float32 [2][slots][taps-1][W]; the step reads buffer `phase` and writes buffer
  * `1 - phase` with the last taps-1 rows of h of every segment (older rows are carried over).
  * y row p of token t is y + t * y_tok_stride + p * y_part_stride (elements); part weights y_w (float32
- * [ntok, y_parts], NULL = ones) multiply each part before the sum. W <= 16384, taps <= 8. */
+ * [ntok, y_parts], NULL = ones) multiply each part before the sum. W <= 16384, taps <= 8.
+ * scratch (float32 [ntok, W], may be NULL): with it, batches of 256 tokens or more that have a convolution run as two
+ * launches over independent rows (both norms of a row; then the convolution over the normalised rows), same results. */
 int qspec_seq_norm_conv(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
                         long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
                         const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok,
-                        int W, float eps, int dtype, void* stream);
+                        int W, float eps, float* scratch, int dtype, void* stream);
 
 /* In-place per-head norm of the query and key sections of a fused projection buffer:
  * row t = [q (H x D) | k (G x D) | v ...] with leading dimension ld; head <- unit_rms(head) * w. */

@@ -111,7 +111,7 @@ SEQ_SIGNATURES = {
     "qspec_launch_count": (c_uint64, []),
     "qspec_seq_embed": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "qspec_seq_norm_conv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p]),
+                                    c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p]),
     "qspec_seq_qk_norm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "qspec_seq_chunk_attention": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]),

@@ -134,8 +134,9 @@ def _kernel_table(torch, s, hbm_gbs, bf16_tflops):
         w1, w2 = torch.zeros(W, device=dev), torch.zeros(W, device=dev)
         cw = torch.randn(W, 4, device=dev) * 0.1
         tail = torch.zeros(2, nslots, 3, W, device=dev)
+        scr = torch.empty(T * W, device=dev)
         us = _time_us(torch, [lambda i=i: ops.seq_norm_conv(x[i], tab, 1e-5, out=h[i], pre_w=w1, conv_w=cw, tail=tail, y=y[i], post_w=w2,
-                                                            x_out=xo[i]) for i in range(nbuf)])
+                                                            x_out=xo[i], scratch=scr) for i in range(nbuf)])
         add("seq_norm_conv (residual + 2 norms + conv)", f"{label} T={T} W={W}", us, nbytes=T * W * 12)
         qkv = [(torch.randn(T, ld, device=dev) * 0.3).to(bf) for _ in range(nbuf)]
         qn = torch.ones(D, device=dev)

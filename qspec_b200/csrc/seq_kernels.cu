@@ -199,6 +199,133 @@ norm_conv_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, cons
   }
 }
 
+// ---- the same for long prompts, in two passes ---------------------------------------------------------------------
+// norm_conv_kernel walks the rows of its run one after the other, two dependent block reductions per row, and so runs at
+// the latency of that chain. With many tokens the work splits into (1) norm_rows_kernel: one CTA per token, the row in
+// registers through both norms, no row depends on another; normalised rows go to a float32 scratch [ntok, W]; and
+// (2) conv_rows_kernel: element-wise convolution over the scratch rows (rows before the segment from the tail), output
+// and tail update. Column assignment and reduction order are those of norm_conv_kernel, so both forms agree bit for bit.
+template <typename T, int VEC, int NV>
+__global__ void __launch_bounds__(256)
+norm_rows_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const T* __restrict__ y, int y_parts,
+                 long long y_part_stride, long long y_tok_stride, const float* __restrict__ y_w,
+                 const float* __restrict__ post_w, const float* __restrict__ pre_w, float* __restrict__ nrm, int W, float eps) {
+  pdl_enter();
+  __shared__ float red[8];
+  const int u = blockIdx.x, tid = threadIdx.x;
+  const float inv_w = 1.0f / (float)W;
+  const float* xr = x_in + (size_t)u * W;
+  VecF<VEC> v[NV];
+  if (y) {
+    float ss = 0.f;
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+      const int c = (tid + q * 256) * VEC;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) v[q].v[e] = 0.f;
+      if (c < W) {
+        for (int p = 0; p < y_parts; ++p) {
+          const VecF<VEC> e = ldv<VEC>(y + (size_t)u * y_tok_stride + (size_t)p * y_part_stride + c);
+          const float pw = y_w ? y_w[(size_t)u * y_parts + p] : 1.0f;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) v[q].v[k] += pw * e.v[k];
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) ss += v[q].v[k] * v[q].v[k];
+      }
+    }
+    const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+      const int c = (tid + q * 256) * VEC;
+      if (c < W) {
+        const VecF<VEC> xv = ldv<VEC>(xr + c), pw = ldv<VEC>(post_w + c);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[q].v[k] = xv.v[k] + v[q].v[k] * r * (1.0f + pw.v[k]);
+        stv<VEC>(x_out + (size_t)u * W + c, v[q]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+      const int c = (tid + q * 256) * VEC;
+      if (c < W) {
+        v[q] = ldv<VEC>(xr + c);
+        if (x_out && x_out != x_in) stv<VEC>(x_out + (size_t)u * W + c, v[q]);
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int q = 0; q < NV; ++q)
+    if ((tid + q * 256) * VEC < W) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) ss += v[q].v[k] * v[q].v[k];
+    }
+  const float r = 1.0f / sqrtf(block_sum_256(ss, red) * inv_w + eps);
+#pragma unroll
+  for (int q = 0; q < NV; ++q) {
+    const int c = (tid + q * 256) * VEC;
+    if (c < W) {
+      const VecF<VEC> pw = ldv<VEC>(pre_w + c);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[q].v[k] = v[q].v[k] * r * (1.0f + pw.v[k]);
+      stv<VEC>(nrm + (size_t)u * W + c, v[q]);
+    }
+  }
+}
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+conv_rows_kernel(const float* __restrict__ nrm, const float* __restrict__ conv_w, int taps, float* __restrict__ tail, int slots,
+                 T* __restrict__ out, const int* __restrict__ meta, int ntok, int W) {
+  pdl_enter();
+  const int u = blockIdx.x, tid = threadIdx.x, hist = taps - 1;
+  const size_t tail_buf = (size_t)slots * hist * W;
+  const TokMeta m = load_meta(meta, ntok, u);
+  const int pos_start = m.pos - (u - m.seg_begin);
+  const float* tail_rd = tail + (size_t)m.phase * tail_buf + (size_t)m.slot * hist * W;
+  float* tail_wr = tail + (size_t)(1 - m.phase) * tail_buf + (size_t)m.slot * hist * W;
+  const float* hrow = nrm + (size_t)u * W;
+  for (int c = tid * VEC; c < W; c += 256 * VEC) {
+    VecF<VEC> v = ldv<VEC>(hrow + c);
+    for (int j = 0; j < taps; ++j) {
+      VecF<VEC> src;
+      const int uu = u - j;
+      if (uu >= m.seg_begin) src = ldv<VEC>(nrm + (size_t)uu * W + c);
+      else {
+        const int pu = m.pos - j;
+        if (pu >= 0) src = ldv<VEC>(tail_rd + (size_t)(pu - (pos_start - hist)) * W + c);
+        else {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) src.v[k] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v.v[k] += conv_w[(size_t)(c + k) * taps + (taps - 1 - j)] * src.v[k];
+    }
+    stv<VEC>(out + (size_t)u * W + c, v);
+  }
+  const int pos_end = pos_start + (m.seg_end - m.seg_begin);      // new tail row r holds position pos_end - hist + r
+  const int my_row = m.pos - (pos_end - hist);
+  if (my_row >= 0)
+    for (int c = tid * VEC; c < W; c += 256 * VEC) stv<VEC>(tail_wr + (size_t)my_row * W + c, ldv<VEC>(hrow + c));
+  if (u == m.seg_begin) {                                         // rows older than the segment are carried over
+    for (int r2 = 0; r2 < hist; ++r2) {
+      const int p = pos_end - hist + r2;
+      if (p >= pos_start) break;
+      const int ro = p - (pos_start - hist);
+      for (int c = tid * VEC; c < W; c += 256 * VEC) {
+        VecF<VEC> v;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v.v[k] = 0.f;
+        if (p >= 0) v = ldv<VEC>(tail_rd + (size_t)ro * W + c);
+        stv<VEC>(tail_wr + (size_t)r2 * W + c, v);
+      }
+    }
+  }
+}
+
 // ---- per-head query / key norm ----------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -645,10 +772,37 @@ static int launch_norm_conv(const float* x_in, float* x_out, const void* y, int 
   return QSPEC_OK;
 }
 
+template <typename T, int VEC, int NV>
+static int launch_norm_rows(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                            long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
+                            const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok, int W,
+                            float eps, float* scratch, cudaStream_t st) {
+  launch_pdl(norm_rows_kernel<T, VEC, NV>, dim3(ntok), dim3(256), 0, st, x_in, x_out, (const T*)y, y_parts, y_part_stride,
+             y_tok_stride, y_w, post_w, pre_w, scratch, W, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  launch_pdl(conv_rows_kernel<T, VEC>, dim3(ntok), dim3(256), 0, st, (const float*)scratch, conv_w, taps, tail, slots, (T*)out, meta,
+             ntok, W);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+template <typename T, int VEC>
+static int launch_norm_rows_nv(int nv, const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                               long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
+                               const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok, int W,
+                               float eps, float* scratch, cudaStream_t st) {
+#define NR_ARGS x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps, tail, slots, out, meta, ntok, W, eps, scratch, st
+  if (nv <= 1) return launch_norm_rows<T, VEC, 1>(NR_ARGS);
+  if (nv <= 2) return launch_norm_rows<T, VEC, 2>(NR_ARGS);
+  if (nv <= 4) return launch_norm_rows<T, VEC, 4>(NR_ARGS);
+  return launch_norm_rows<T, VEC, 8>(NR_ARGS);
+#undef NR_ARGS
+}
+
 extern "C" int qspec_seq_norm_conv(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
                                    long long y_tok_stride, const float* y_w, const float* post_w, const float* pre_w,
                                    const float* conv_w, int taps, float* tail, int slots, void* out, const int* meta, int ntok,
-                                   int W, float eps, int dtype, void* stream) {
+                                   int W, float eps, float* scratch, int dtype, void* stream) {
   QSPEC_REQUIRE(x_in && meta, QSPEC_ERR_INVALID_ARG, "seq_norm_conv: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && W > 0 && W <= 16384, QSPEC_ERR_UNSUPPORTED, "seq_norm_conv: width %d (1..16384)", W);
   QSPEC_REQUIRE(!y || (x_out && x_out != x_in && post_w && y_parts >= 1), QSPEC_ERR_INVALID_ARG,
@@ -665,6 +819,16 @@ extern "C" int qspec_seq_norm_conv(const float* x_in, float* x_out, const void* 
   const bool al = W % 4 == 0 && y_part_stride % 4 == 0 && y_tok_stride % 4 == 0 &&
                   (((uintptr_t)x_in | (uintptr_t)x_out | (uintptr_t)y | (uintptr_t)out | (uintptr_t)tail | (uintptr_t)post_w |
                     (uintptr_t)pre_w) & 15) == 0;
+  // long prompts with a convolution: two passes over independent rows (scratch: float32 [ntok, W]) once a row fits the
+  // registers of its CTA
+  const int vecw = al && ((uintptr_t)scratch & 15) == 0 ? 4 : 1;
+  const int nv = (W + 256 * vecw - 1) / (256 * vecw);
+  if (scratch && out && conv_w && taps > 1 && ntok >= 256 && nv <= 8) {
+#define NR2_ARGS nv, x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps, tail, slots, out, meta, ntok, W, eps, scratch, (cudaStream_t)stream
+    if (dtype == QSPEC_DTYPE_F32) return vecw == 4 ? launch_norm_rows_nv<float, 4>(NR2_ARGS) : launch_norm_rows_nv<float, 1>(NR2_ARGS);
+    return vecw == 4 ? launch_norm_rows_nv<__nv_bfloat16, 4>(NR2_ARGS) : launch_norm_rows_nv<__nv_bfloat16, 1>(NR2_ARGS);
+#undef NR2_ARGS
+  }
 #define NC_ARGS x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, post_w, pre_w, conv_w, taps, tail, slots, out, meta, ntok, W, eps, (cudaStream_t)stream
   if (dtype == QSPEC_DTYPE_F32) return al ? launch_norm_conv<float, 4>(NC_ARGS) : launch_norm_conv<float, 1>(NC_ARGS);
   return al ? launch_norm_conv<__nv_bfloat16, 4>(NC_ARGS) : launch_norm_conv<__nv_bfloat16, 1>(NC_ARGS);

@@ -251,6 +251,7 @@ class MutusunModel(torch.nn.Module):
         mx = lambda vals: max(list(vals) + [1])
         self.buf_x = [torch.empty(T * W, **f32), torch.empty(T * W, **f32)]          # residual stream, ping-pong
         self.buf_h = torch.empty(T * W, **act)
+        self.buf_n = torch.empty(T * W, **f32)                                        # normalised rows of long prompts (seq_norm_conv)
         self.buf_qkv = torch.empty(T * mx(l.mixer.ld for l in cfg.layers), **act)
         self.buf_att = torch.empty(T * mx(l.mixer.heads * l.mixer.vdim for l in cfg.layers), **act)
         self.buf_y = [torch.empty(T * W, **act), torch.empty(T * W, **act)]          # mixer / feed-forward outputs
@@ -304,10 +305,10 @@ class MutusunModel(torch.nn.Module):
         def enter(pre_w, conv_w, tail, out):
             nonlocal xa, xb, pend
             if pend is None:
-                ops.seq_norm_conv(xa, tab, eps, out=out, pre_w=pre_w, conv_w=conv_w, tail=tail)
+                ops.seq_norm_conv(xa, tab, eps, out=out, pre_w=pre_w, conv_w=conv_w, tail=tail, scratch=self.buf_n)
             else:
                 ops.seq_norm_conv(xa, tab, eps, out=out, pre_w=pre_w, conv_w=conv_w, tail=tail, y=pend[0], y_w=pend[1],
-                                  post_w=pend[2], x_out=xb)
+                                  post_w=pend[2], x_out=xb, scratch=self.buf_n)
                 xa, xb = xb, xa
                 pend = None
 

@@ -771,11 +771,14 @@ def seq_embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
 def seq_norm_conv(x_in: torch.Tensor, meta: torch.Tensor, eps: float, *, out: Optional[torch.Tensor] = None,
                   pre_w: Optional[torch.Tensor] = None, conv_w: Optional[torch.Tensor] = None,
                   tail: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None, y_w: Optional[torch.Tensor] = None,
-                  post_w: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None) -> None:
+                  post_w: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None,
+                  scratch: Optional[torch.Tensor] = None) -> None:
     """Closes a sublayer (x_out = x_in + zero-centred norm of y, with weight post_w) and opens the next
     (out = h + causal short convolution of h, h = zero-centred norm of the new residual with weight pre_w) in one launch.
     y: [ntok, W] or [ntok, parts, W] (parts summed, each times y_w [ntok, parts] if given). tail: float32
-    [2, slots, taps-1, W], read at meta's phase, written at the other. out None: only the residual sum."""
+    [2, slots, taps-1, W], read at meta's phase, written at the other. out None: only the residual sum.
+    scratch: float32 with room for [ntok, W]; with it, long prompts (256 tokens or more) run as two launches over
+    independent rows instead of one that walks the rows of a run in turn; same results."""
     _chk(x_in, "x_in", (_F32,)); _chk(meta, "meta", (torch.int32,))
     ntok, W = x_in.shape
     if meta.shape != (5, ntok):
@@ -796,9 +799,13 @@ def seq_norm_conv(x_in: torch.Tensor, meta: torch.Tensor, eps: float, *, out: Op
             raise ValueError("seq_norm_conv: tail must be float32 [2, slots, taps-1, W]")
         slots = tail.shape[1]
     act = out if out is not None else y
+    if scratch is not None:
+        _chk(scratch, "scratch", (_F32,))
+        if scratch.numel() < ntok * W:
+            raise ValueError("seq_norm_conv: scratch is smaller than [ntok, W]")
     _seq(_lib.load_seq().qspec_seq_norm_conv(_ptr(x_in), _ptr(x_out), _ptr(y), parts, pstride, tstride, _ptr(y_w), _ptr(post_w),
                                              _ptr(pre_w), _ptr(conv_w), taps, _ptr(tail), slots, _ptr(out), _ptr(meta), ntok, W,
-                                             float(eps), _sdt(act), _stream()), "seq_norm_conv")
+                                             float(eps), _ptr(scratch), _sdt(act), _stream()), "seq_norm_conv")
 
 
 def seq_qk_norm(qkv: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, H: int, G: int, D: int, eps: float) -> None:

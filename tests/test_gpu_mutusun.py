@@ -84,6 +84,65 @@ def test_norm_conv_with_tail_over_portions(dtype, W, taps):
         close(torch.cat(got), want, dtype)
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("W,taps,parts", [(96, 3, 1), (257, 4, 1), (1024, 2, 3), (2100, 5, 1)])
+def test_norm_conv_of_long_prompts_in_two_passes(dtype, W, taps, parts):
+    """256 tokens or more with a scratch buffer take the two-launch form (rows independent, then the convolution): two
+    sequences in one batch, each continued from an earlier portion whose tail it reads (the other tail buffer is NaN-filled),
+    one of them still in its first taps - 1 positions; against the plain implementation and, bit for bit, the one-launch form."""
+    _cuda()
+    from qspec_b200 import ops
+    g = torch.Generator().manual_seed(W + taps)
+    eps, hist = 1e-5, taps - 1
+    lens = {0: (1, 150), 2: (7, 130)}                        # slot -> (first portion, second portion)
+    seqs = {}
+    for slot, (n0, n1) in lens.items():
+        T = n0 + n1
+        x = (torch.randn(T, W, generator=g) * 3).double()
+        yp = torch.randn(T, parts, W, generator=g)
+        yp = bf16_round(yp) if dtype == BF16 else yp.double()
+        yw = torch.rand(T, parts, generator=g).double() if parts > 1 else torch.ones(T, 1, dtype=torch.float64)
+        seqs[slot] = (x, yp, yw)
+    post_w, pre_w = [0.3 * torch.randn(W, generator=g).double() for _ in range(2)]
+    cw = 0.5 * torch.randn(W, taps, generator=g).double()
+    want = {}
+    for slot, (x, yp, yw) in seqs.items():
+        r = x + O.norm_zero_centred((yp.double() * yw[:, :, None]).sum(1), post_w, eps)
+        want[slot] = (r, O.short_conv_residual(O.norm_zero_centred(r, pre_w, eps), cw))
+    dev = lambda t: t.float().cuda()
+    results = []
+    for use_scratch in (True, False):
+        tail = torch.full((2, 3, hist, W), float("nan"), dtype=F32, device="cuda")
+        scratch = torch.full((300 * W,), float("nan"), dtype=F32, device="cuda") if use_scratch else None
+        got = {}
+        for step in (0, 1):
+            segs, xs, ys, ws = [], [], [], []
+            for slot, (n0, n1) in lens.items():
+                a, b = (0, n0) if step == 0 else (n0, n0 + n1)
+                segs.append((slot, a, b - a, step))
+                xs.append(seqs[slot][0][a:b]); ys.append(seqs[slot][1][a:b]); ws.append(seqs[slot][2][a:b])
+            tab = meta_table(segs)
+            x, y, yw = torch.cat(xs), torch.cat(ys), torch.cat(ws)
+            n = x.shape[0]
+            out = torch.empty(n, W, dtype=dtype, device="cuda")
+            xo = torch.empty(n, W, dtype=F32, device="cuda")
+            ops.seq_norm_conv(dev(x), tab, eps, out=out, pre_w=dev(pre_w), conv_w=dev(cw), tail=tail,
+                              y=(y if parts > 1 else y[:, 0]).to(dtype).cuda().contiguous(), y_w=dev(yw) if parts > 1 else None,
+                              post_w=dev(post_w), x_out=xo, scratch=scratch)
+            if step == 1:
+                at = 0
+                for slot, (n0, n1) in lens.items():
+                    got[slot] = (xo[at:at + n1].cpu(), out[at:at + n1].float().cpu())
+                    at += n1
+        for slot, (n0, n1) in lens.items():
+            close(got[slot][0], want[slot][0][n0:], F32)
+            close(got[slot][1], want[slot][1][n0:], dtype)
+        results.append((got, tail[0][[0, 2]].clone()))        # the second step read tail buffer 1 and wrote buffer 0
+    for slot in lens:
+        assert torch.equal(results[0][0][slot][0], results[1][0][slot][0]) and torch.equal(results[0][0][slot][1], results[1][0][slot][1])
+    assert not torch.isnan(results[0][1]).any() and torch.equal(results[0][1], results[1][1])
+
+
 def test_norm_conv_partial_sums_and_weights():
     """The pending output given as weighted parts (mixture-of-experts form) equals the weighted sum given whole."""
     _cuda()
