@@ -106,6 +106,87 @@ int qspec_moe_expert_grouped(const void* h, const void* gate_up, const void* dow
                              void* stream);
 int qspec_moe_expert_grouped_supported(int W, int F);
 
+/* Router that softmaxes over the chosen outputs only: z = router_w h (float32), the `top` largest z (lowest index among
+ * equals) -> idx, weight = softmax over those `top` logits. */
+int qspec_moe_route_chosen(const void* h, const float* router_w, int* idx, float* weight, int ntok, int W, int R, int top,
+                           int dtype, void* stream);
+
+/* Expert activations of the two expert kernels below. GATED: [gate ; up] rows, the clamped gated form described at
+ * qspec_moe_expert_tokens. RELU2: up rows only (weights [E, F, W]), y = max(up h, 0)^2; `limit` is ignored. */
+#define QSPEC_EXPERT_ACT_GATED 0
+#define QSPEC_EXPERT_ACT_RELU2 1
+int qspec_moe_expert_tokens_act(const void* h, const void* up, const void* down, const int* idx, void* out, int ntok, int W,
+                                int F, int E, int top, float limit, int act, int dtype, void* stream);
+int qspec_moe_expert_grouped_act(const void* h, const void* up, const void* down, const int* idx, void* out, int ntok, int W,
+                                 int F, int E, int top, float limit, int act, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+
+/* ---- mixers whose state outlives a chunk: token shift, windowed softmax attention with a sink (latent or grouped-query
+ * keys), gated linear recurrence. Ring caches: row = position % cap; the step's own rows are written before they are read,
+ * so cap >= window - 1 + (tokens of one sequence in a step). ---- */
+
+/* out_t = x_t + (x_(t-1) - x_t) * shift. The row before a segment's first token is prev[phase][slot] (zero at position
+ * 0); the segment's last row goes to prev[1 - phase][slot]. prev: float32 [2][slots][W]. */
+int qspec_seq_token_shift(const float* x, const float* shift, float* prev, int slots, void* out, const int* meta, int ntok,
+                          int W, int dtype, void* stream);
+
+/* r = x_in + norm(v), v = sum_p y_w[t, p] * y[t, p, :] (y_w NULL: ones). kind 0: layer norm (v - mean) / sqrt(var + eps)
+ * * w + b with var the mean of the squared deviations; kind 1: v / sqrt(mean(v^2) + eps) * w (+ b if given).
+ * x_in NULL: r = norm(v). r goes to x_out (float32, may alias x_in, may be NULL) and, cast, to out (may be NULL).
+ * y has element type y_dtype: the activation type or float32. */
+int qspec_seq_add_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                       long long y_tok_stride, const float* y_w, const float* w, const float* b, int kind, void* out, int ntok,
+                       int W, float eps, int y_dtype, int dtype, void* stream);
+
+/* Latent attention, after the down projections. Row t of d (leading dimension ld): [query latent (q_rank) | key/value
+ * latent (kv_rank) | shared rotary key part (rot_dim)]. cq[t] = unit_rms(query latent) * qn_w. With a cache (the layer
+ * owns one; otherwise cache == NULL and the row holds the query latent only): cache[slot, pos % cap] =
+ * [unit_rms(key/value latent) * kvn_w | rotate(rotary key part)], row length kv_rank + rot_dim. The rotation turns the
+ * pair (i, i + rot_dims/2) of the first rot_dims entries by the angle pos * inv_freq[i] (float32). */
+int qspec_seq_latent_prep(const void* d, int ld, int q_rank, int kv_rank, int rot_dim, const float* qn_w, const float* kvn_w,
+                          const float* inv_freq, int rot_dims, void* cq, void* cache, int cap, const int* meta, int ntok,
+                          float eps, int dtype, void* stream);
+
+/* dst[t, h, 0:n] (float32) = rotate(src[t, h, off : off + n]): strides in elements; the first rot_dims entries rotated as
+ * above, the rest copied. */
+int qspec_seq_rotary(const void* src, long long src_tok_stride, int src_head_stride, int off, float* dst,
+                     long long dst_tok_stride, int dst_head_stride, int H, int n, int rot_dims, const float* inv_freq,
+                     const int* meta, int ntok, int dtype, void* stream);
+
+/* Grouped-query attention, after the fused projection (biases added): row t of p = [q (HD) | k (GD) | v (GDV) | ...].
+ * qout[t] (float32) = unit_rms(q over all HD entries) * qn_w; cache_k[slot, pos % cap] = unit_rms(k over all GD entries)
+ * * kn_w; cache_v[slot, pos % cap] = v. */
+int qspec_seq_qkv_prep(const void* p, int ld, int HD, int GD, int GDV, const float* qn_w, const float* kn_w, float* qout,
+                       void* cache_k, void* cache_v, int cap, const int* meta, int ntok, float eps, int dtype, void* stream);
+
+/* Sliding-window softmax attention with a sink. Token at position i sees keys j with 0 <= i - j < window; the weights are
+ * exp(score_j) / (sum_j exp(score_j) + exp(sink[h])), score = scale * (qa . key[0:DA] + qb . key[DA:DA+DB]). Queries are
+ * float32 with free token / head strides (elements). Key of (slot, position j, key/value head g) lies at
+ * k + slot * k_slot_stride + (j % cap) * k_row_stride + g * k_head_stride, values likewise (a latent cache passes the
+ * same buffer twice with G = 1). Query head h uses key/value head h / (H / G). gate (may be NULL): the output is
+ * multiplied by sigmoid(gate[t, h * DV + d]). out [ntok, H, DV]. sink may be NULL (no sink). DV <= 512. */
+typedef struct qspec_window_attn_args {
+  const float* qa; long long qa_tok_stride, qa_head_stride; int DA;
+  const float* qb; long long qb_tok_stride, qb_head_stride; int DB;
+  const void* k; long long k_slot_stride; int k_row_stride, k_head_stride;
+  const void* v; long long v_slot_stride; int v_row_stride, v_head_stride; int DV;
+  const float* sink; const void* gate; int gate_ld;
+  void* out; const int* meta; int ntok, H, G, window, cap; float scale;
+} qspec_window_attn_args;
+int qspec_seq_window_attention(const qspec_window_attn_args* args, int dtype, void* stream);
+
+/* HGRN2 recurrence. Row t of p = [zq (H x D) | zf (H x D) | v (H x DV)]. q = silu(zq), f = lower + (1 - lower) *
+ * sigmoid(zf + f_b); per head S <- diag(f) S + (1 - f) v^T, o = S^T q; out[t, h] = unit_rms(o over DV) * norm_w.
+ * state: float32 [slots, H, D, DV], read at a segment's start (zero at position 0), written at its end.
+ * scratch: float32 [ntok, H * DV]. D <= 256. */
+int qspec_seq_hgrn2(const void* p, int ld, const float* f_b, const float* lower, const float* norm_w, float* state,
+                    float* scratch, void* out, const int* meta, int ntok, int H, int D, int DV, float eps, int dtype,
+                    void* stream);
+
+/* g[t, :] <- gelu_tanh(g[t, :]) * table[ids[t], col0 : col0 + sd]  (g [ntok, sd], table [V, table_ld]). */
+int qspec_seq_side_gate(void* g, const void* table, const int* ids, int col0, int sd, int table_ld, int V, int ntok, int dtype,
+                        void* stream);
+
 /* Arg max per row of float32 / bfloat16 logits [rows, V] (lowest index among equal maxima): int64 out. */
 int qspec_seq_argmax_rows(const void* logits, int rows, int V, long long row_stride, long long* out_idx, int dtype,
                           void* stream);

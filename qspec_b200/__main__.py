@@ -30,7 +30,7 @@ def _generate(argv) -> int:
     from .build import build_library, build_seq_library
     arch = registry.architecture_of(registry.read_config(args.model))
     build_seq_library()
-    if arch != "Mutusun":
+    if arch not in ("Mutusun", "Pitudra"):
         build_library()
     from .scheduler import Scheduler
     model = registry.load_model(args.model, dtype=args.dtype, n_slots=args.slots, max_step_tokens=args.step_tokens)

@@ -129,7 +129,36 @@ SEQ_SIGNATURES = {
     "qspec_moe_grouped_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "qspec_moe_expert_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_float, c_void_p, c_size_t, c_void_p]),
+    "qspec_moe_route_chosen": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "qspec_moe_expert_tokens_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                            c_float, c_int, c_int, c_void_p]),
+    "qspec_moe_expert_grouped_act": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                             c_float, c_int, c_void_p, c_size_t, c_void_p]),
+    "qspec_seq_token_shift": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "qspec_seq_add_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                   c_int, c_int, c_float, c_int, c_int, c_void_p]),
+    "qspec_seq_latent_prep": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                      c_int, c_void_p, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_rotary": (c_int, [c_void_p, c_ll, c_int, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                 c_int, c_void_p]),
+    "qspec_seq_qkv_prep": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_window_attention": (c_int, [c_void_p, c_int, c_void_p]),
+    "qspec_seq_hgrn2": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                c_int, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_side_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
 }
+
+
+class WindowAttnArgs(ctypes.Structure):
+    """qspec_window_attn_args of include/qspec_b200_seq.h."""
+    _fields_ = [("qa", c_void_p), ("qa_tok_stride", c_ll), ("qa_head_stride", c_ll), ("DA", c_int),
+                ("qb", c_void_p), ("qb_tok_stride", c_ll), ("qb_head_stride", c_ll), ("DB", c_int),
+                ("k", c_void_p), ("k_slot_stride", c_ll), ("k_row_stride", c_int), ("k_head_stride", c_int),
+                ("v", c_void_p), ("v_slot_stride", c_ll), ("v_row_stride", c_int), ("v_head_stride", c_int), ("DV", c_int),
+                ("sink", c_void_p), ("gate", c_void_p), ("gate_ld", c_int),
+                ("out", c_void_p), ("meta", c_void_p), ("ntok", c_int), ("H", c_int), ("G", c_int), ("window", c_int),
+                ("cap", c_int), ("scale", c_float)]
 
 _lib = None
 _seq_lib = None

@@ -4,7 +4,7 @@
 // weights (bfloat16 / float32); every reduction, exponential and the residual stream are float32 in both.
 #include <cstdlib>
 #include <cstring>
-#include "common.cuh"
+#include "seq_common.cuh"
 #include "../../include/qspec_b200_seq.h"
 
 namespace qspec {
@@ -13,25 +13,6 @@ namespace qspec {
 int chunk_attention_token_mma(const void* qkv, int ld, const void* ck, const void* cv, const float* bias, void* out, const int* meta,
                               int ntok, int H, int G, int D, int DV, int size, float scale, float softcap, int max_keys,
                               cudaStream_t st);
-
-__device__ __forceinline__ float to_f(float v) { return v; }
-__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <typename T> __device__ __forceinline__ T from_f(float v);
-template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
-template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-
-struct TokMeta {
-  int slot, pos, seg_begin, seg_end, phase;
-};
-__device__ __forceinline__ TokMeta load_meta(const int* meta, int ntok, int i) {
-  TokMeta m;
-  m.slot = meta[i];
-  m.pos = meta[ntok + i];
-  m.seg_begin = meta[2 * ntok + i];
-  m.seg_end = meta[3 * ntok + i];
-  m.phase = meta[4 * ntok + i];
-  return m;
-}
 
 // ---- embedding ------------------------------------------------------------------------------------------------
 template <typename T>
@@ -50,36 +31,6 @@ __global__ void __launch_bounds__(256) embed_kernel(const T* __restrict__ table,
 // taps-1 tokens: rows inside the step's segment are kept in a shared-memory ring (the CTA first recomputes the taps-1
 // rows in front of its run), rows before the segment come from the per-slot tail. Every thread owns the same columns in
 // all rows, so the ring needs no barriers beyond those of the two row reductions. VEC = 4: 16-byte accesses (W % 4 == 0).
-template <int VEC> struct VecF { float v[VEC]; };
-template <int VEC> __device__ __forceinline__ VecF<VEC> ldv(const float* p) {
-  VecF<VEC> r;
-  if (VEC == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[1 % VEC] = t.y; r.v[2 % VEC] = t.z; r.v[3 % VEC] = t.w; }
-  else r.v[0] = *p;
-  return r;
-}
-template <int VEC> __device__ __forceinline__ VecF<VEC> ldv(const __nv_bfloat16* p) {
-  VecF<VEC> r;
-  if (VEC == 4) {
-    const uint2 t = *reinterpret_cast<const uint2*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
-    r.v[0] = a.x; r.v[1 % VEC] = a.y; r.v[2 % VEC] = b.x; r.v[3 % VEC] = b.y;
-  } else r.v[0] = __bfloat162float(*p);
-  return r;
-}
-template <int VEC> __device__ __forceinline__ void stv(float* p, const VecF<VEC>& r) {
-  if (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1 % VEC], r.v[2 % VEC], r.v[3 % VEC]);
-  else *p = r.v[0];
-}
-template <int VEC> __device__ __forceinline__ void stv(__nv_bfloat16* p, const VecF<VEC>& r) {
-  if (VEC == 4) {
-    uint2 t;
-    *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(r.v[0], r.v[1 % VEC]);
-    *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(r.v[2 % VEC], r.v[3 % VEC]);
-    *reinterpret_cast<uint2*>(p) = t;
-  } else *p = __float2bfloat16_rn(r.v[0]);
-}
-
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 norm_conv_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const T* __restrict__ y, int y_parts,
@@ -589,7 +540,7 @@ __global__ void __launch_bounds__(256) relu2_kernel(T* __restrict__ a, long long
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float* __restrict__ corr, int* __restrict__ idx,
-             float* __restrict__ weight, int W, int R, int top) {
+             float* __restrict__ weight, int W, int R, int top, int chosen_only) {
   pdl_enter();
   extern __shared__ float sm_rt[];            // z [R] | choice [R]
   float* z = sm_rt;
@@ -619,6 +570,35 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
   }
   __syncthreads();
   if (warp != 0) return;
+  if (chosen_only) {
+    // the `top` largest logits, then a softmax over those alone (the first pick is their maximum)
+    float first = 0.f, sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int r = lane; r < R; r += 32)
+        if (z[r] > bv) { bv = z[r]; bi = r; }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (bi >= R) bi = 0;
+      if (k == 0) first = bv;
+      const float e = expf(bv - first);
+      sum += e;
+      if (lane == 0) {
+        idx[(size_t)i * top + k] = bi;
+        weight[(size_t)i * top + k] = e;
+        z[bi] = -INFINITY;
+      }
+      __syncwarp();
+    }
+    if (lane == 0)
+      for (int k = 0; k < top; ++k) weight[(size_t)i * top + k] /= sum;
+    return;
+  }
   float mx = -INFINITY;
   for (int r = lane; r < R; r += 32) mx = fmaxf(mx, z[r]);
   mx = warp_xor_max(mx);
@@ -660,7 +640,7 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
 template <typename T>
 __global__ void __launch_bounds__(256)
 expert_tokens_kernel(const T* __restrict__ h, const T* __restrict__ gate_up, const T* __restrict__ down,
-                     const int* __restrict__ idx, T* __restrict__ out, int W, int F, int E, int top, float limit) {
+                     const int* __restrict__ idx, T* __restrict__ out, int W, int F, int E, int top, float limit, int act) {
   pdl_enter();
   extern __shared__ float sm_ex[];            // h [W] | y [F]
   float* sh = sm_ex;
@@ -675,8 +655,19 @@ expert_tokens_kernel(const T* __restrict__ h, const T* __restrict__ gate_up, con
   }
   for (int c = tid; c < W; c += 256) sh[c] = to_f(hp[c]);
   __syncthreads();
-  const T* wg = gate_up + (size_t)e * 2 * F * W;
+  const T* wg = gate_up + (size_t)e * (act == QSPEC_EXPERT_ACT_RELU2 ? 1 : 2) * F * W;
   const T* wu = wg + (size_t)F * W;
+  if (act == QSPEC_EXPERT_ACT_RELU2) {
+    for (int f = warp; f < F; f += 8) {
+      float au = 0.f;
+      for (int c = lane; c < W; c += 32) au += to_f(wg[(size_t)f * W + c]) * sh[c];
+      au = warp_xor_sum(au);
+      if (lane == 0) {
+        const float u = fmaxf(to_f(from_f<T>(au)), 0.f);
+        sy[f] = to_f(from_f<T>(u * u));
+      }
+    }
+  } else
   for (int f = warp; f < F; f += 8) {
     float ag = 0.f, au = 0.f;
     for (int c = lane; c < W; c += 32) {
@@ -980,9 +971,9 @@ extern "C" int qspec_seq_relu2(void* a, long long n, int dtype, void* stream) {
   return QSPEC_OK;
 }
 
-extern "C" int qspec_moe_route(const void* h, const float* router_w, const float* correction, int* idx, float* weight, int ntok, int W,
-                               int R, int top, int dtype, void* stream) {
-  QSPEC_REQUIRE(h && router_w && correction && idx && weight, QSPEC_ERR_INVALID_ARG, "moe_route: null pointer");
+static int route_any(const void* h, const float* router_w, const float* correction, int* idx, float* weight, int ntok, int W, int R, int top,
+                     int chosen_only, int dtype, void* stream) {
+  QSPEC_REQUIRE(h && router_w && (correction || chosen_only) && idx && weight, QSPEC_ERR_INVALID_ARG, "moe_route: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && W > 0 && R > 0 && R <= 1024 && top >= 1 && top <= 32 && top <= R, QSPEC_ERR_UNSUPPORTED,
                 "moe_route: %d router outputs (<= 1024), top %d (<= 32)", R, top);
   SEQ_DTYPE_OK(dtype);
@@ -990,16 +981,27 @@ extern "C" int qspec_moe_route(const void* h, const float* router_w, const float
   const size_t smem = (size_t)2 * R * sizeof(float);
   if (dtype == QSPEC_DTYPE_F32)
     launch_pdl(route_kernel<float>, dim3(ntok), dim3(128), smem, (cudaStream_t)stream, (const float*)h, router_w, correction, idx,
-               weight, W, R, top);
+               weight, W, R, top, chosen_only);
   else
     launch_pdl(route_kernel<__nv_bfloat16>, dim3(ntok), dim3(128), smem, (cudaStream_t)stream, (const __nv_bfloat16*)h, router_w,
-               correction, idx, weight, W, R, top);
+               correction, idx, weight, W, R, top, chosen_only);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
 
-extern "C" int qspec_moe_expert_tokens(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok, int W,
-                                       int F, int E, int top, float limit, int dtype, void* stream) {
+extern "C" int qspec_moe_route(const void* h, const float* router_w, const float* correction, int* idx, float* weight, int ntok, int W,
+                               int R, int top, int dtype, void* stream) {
+  return route_any(h, router_w, correction, idx, weight, ntok, W, R, top, 0, dtype, stream);
+}
+
+extern "C" int qspec_moe_route_chosen(const void* h, const float* router_w, int* idx, float* weight, int ntok, int W, int R, int top,
+                                      int dtype, void* stream) {
+  return route_any(h, router_w, nullptr, idx, weight, ntok, W, R, top, 1, dtype, stream);
+}
+
+extern "C" int qspec_moe_expert_tokens_act(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok, int W,
+                                           int F, int E, int top, float limit, int act, int dtype, void* stream) {
+  QSPEC_REQUIRE(act == QSPEC_EXPERT_ACT_GATED || act == QSPEC_EXPERT_ACT_RELU2, QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: unknown activation %d", act);
   QSPEC_REQUIRE(h && idx && out && (E == 0 || (gate_up && down)), QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && W > 0 && F >= 0 && E >= 0 && top >= 1 && top <= 65535, QSPEC_ERR_INVALID_ARG, "moe_expert_tokens: bad sizes");
   SEQ_DTYPE_OK(dtype);
@@ -1015,12 +1017,17 @@ extern "C" int qspec_moe_expert_tokens(const void* h, const void* gate_up, const
   }
   if (w == 0)
     launch_pdl(expert_tokens_kernel<float>, dim3(ntok, top), dim3(256), smem, (cudaStream_t)stream, (const float*)h,
-               (const float*)gate_up, (const float*)down, idx, (float*)out, W, F, E, top, limit);
+               (const float*)gate_up, (const float*)down, idx, (float*)out, W, F, E, top, limit, act);
   else
     launch_pdl(expert_tokens_kernel<__nv_bfloat16>, dim3(ntok, top), dim3(256), smem, (cudaStream_t)stream, (const __nv_bfloat16*)h,
-               (const __nv_bfloat16*)gate_up, (const __nv_bfloat16*)down, idx, (__nv_bfloat16*)out, W, F, E, top, limit);
+               (const __nv_bfloat16*)gate_up, (const __nv_bfloat16*)down, idx, (__nv_bfloat16*)out, W, F, E, top, limit, act);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
+}
+
+extern "C" int qspec_moe_expert_tokens(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok, int W,
+                                       int F, int E, int top, float limit, int dtype, void* stream) {
+  return qspec_moe_expert_tokens_act(h, gate_up, down, idx, out, ntok, W, F, E, top, limit, QSPEC_EXPERT_ACT_GATED, dtype, stream);
 }
 
 extern "C" int qspec_seq_argmax_rows(const void* logits, int rows, int V, long long row_stride, long long* out_idx, int dtype,

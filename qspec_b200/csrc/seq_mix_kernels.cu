@@ -1,0 +1,592 @@
+// Sequence-mixer kernels, second file (include/qspec_b200_seq.h): token shift with a per-slot previous row, residual sum
+// with a layer norm or unit-RMS norm of the sublayer's OUTPUT, latent (low-rank) key/value preparation with a rotary
+// part, whole-projection query/key norms, sliding-window softmax attention with a per-head sink over a per-slot ring
+// cache (shared by the latent and the grouped-query form), the HGRN2 gated linear recurrence with its state in
+// float32, per-head output norm, and the gated per-token side input. Element type of activations and large weights:
+// bfloat16 or float32; every norm, score, softmax weight, angle, gate of the recurrence and state is float32.
+#include <cstdlib>
+#include "seq_common.cuh"
+#include "../../include/qspec_b200_seq.h"
+
+namespace qspec {
+
+// Pairs of elements per lane where rows allow it (even sizes and strides): 4-byte bfloat16 and 8-byte float32 loads.
+template <int VEC> __device__ __forceinline__ void ld_pair(const float* p, float (&o)[2]) {
+  if (VEC == 2) { const float2 t = *reinterpret_cast<const float2*>(p); o[0] = t.x; o[1] = t.y; }
+  else { o[0] = *p; o[1] = 0.f; }
+}
+template <int VEC> __device__ __forceinline__ void ld_pair(const __nv_bfloat16* p, float (&o)[2]) {
+  if (VEC == 2) { const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); o[0] = t.x; o[1] = t.y; }
+  else { o[0] = __bfloat162float(*p); o[1] = 0.f; }
+}
+
+// ---- token shift --------------------------------------------------------------------------------------------------
+// One CTA per token. The row before a segment's first token is the slot's saved row (buffer `phase`), zero at position
+// 0; a segment's last row is saved to the other buffer, so that no CTA reads what another one of the same step writes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+token_shift_kernel(const float* __restrict__ x, const float* __restrict__ shift, float* __restrict__ prev, int slots,
+                   T* __restrict__ out, const int* __restrict__ meta, int ntok, int W) {
+  pdl_enter();
+  const int i = blockIdx.x;
+  const TokMeta m = load_meta(meta, ntok, i);
+  const float* xr = x + (size_t)i * W;
+  const float* pr = nullptr;
+  if (i > m.seg_begin) pr = xr - W;
+  else if (m.pos > 0) pr = prev + ((size_t)m.phase * slots + m.slot) * W;
+  float* keep = (i == m.seg_end - 1) ? prev + ((size_t)(1 - m.phase) * slots + m.slot) * W : nullptr;
+  T* orow = out + (size_t)i * W;
+  for (int c = threadIdx.x; c < W; c += 256) {
+    const float v = xr[c];
+    const float p = pr ? pr[c] : 0.f;
+    orow[c] = from_f<T>(v + (p - v) * shift[c]);
+    if (keep) keep[c] = v;
+  }
+}
+
+// ---- residual sum with a norm of the sublayer's output ------------------------------------------------------------
+// v = sum of the parts of y (weighted); n = (v - mean) / sqrt(var + eps) * w + b (kind 0) or v / sqrt(mean(v^2) + eps) * w
+// (kind 1); r = x_in + n. The row lives in shared memory between the passes; the variance is the mean of the squared
+// deviations (second pass), not E[v^2] - mean^2.
+template <typename T, typename YT>
+__global__ void __launch_bounds__(256)
+add_norm_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, const YT* __restrict__ y, int y_parts,
+                long long y_part_stride, long long y_tok_stride, const float* __restrict__ y_w, const float* __restrict__ w,
+                const float* __restrict__ b, int kind, T* __restrict__ out, int W, float eps) {
+  pdl_enter();
+  extern __shared__ float sm_an[];            // row [W]
+  __shared__ float red[8];
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const YT* yr = y + (size_t)i * y_tok_stride;
+  float s = 0.f;
+  for (int c = tid; c < W; c += 256) {
+    float v;
+    if (y_parts == 1 && !y_w) {
+      v = to_f(yr[c]);
+    } else {
+      v = 0.f;
+      for (int p = 0; p < y_parts; ++p) v += (y_w ? y_w[(size_t)i * y_parts + p] : 1.0f) * to_f(yr[(size_t)p * y_part_stride + c]);
+    }
+    sm_an[c] = v;
+    s += v;
+  }
+  const float inv_w = 1.0f / (float)W;
+  float mean = 0.f;
+  if (kind == 0) mean = block_sum_256(s, red) * inv_w;
+  float q = 0.f;
+  for (int c = tid; c < W; c += 256) {
+    const float d = sm_an[c] - mean;
+    q += d * d;
+  }
+  const float var = block_sum_256(q, red) * inv_w;
+  const float r = 1.0f / sqrtf(var + eps);
+  for (int c = tid; c < W; c += 256) {
+    float v = (sm_an[c] - mean) * r * w[c];
+    if (b) v += b[c];
+    if (x_in) v += x_in[(size_t)i * W + c];
+    if (x_out) x_out[(size_t)i * W + c] = v;
+    if (out) out[(size_t)i * W + c] = from_f<T>(v);
+  }
+}
+
+// ---- latent attention: norms of the low-rank projections, rotary key part, cache write ----------------------------
+// Row of d: [q latent (q_rank) | kv latent (kv_rank) | shared rotary key part (rot_dim)]; the last two only when the
+// layer owns a cache. One CTA per token. Cache row = position % cap: [normalised kv latent | rotated key part].
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_prep_kernel(const T* __restrict__ d, int ld, int q_rank, int kv_rank, int rot_dim, const float* __restrict__ qn_w,
+                   const float* __restrict__ kvn_w, const float* __restrict__ inv_freq, int rot_dims, T* __restrict__ cq,
+                   T* __restrict__ cache, int cap, const int* __restrict__ meta, int ntok, float eps) {
+  pdl_enter();
+  __shared__ float red[8];
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const T* row = d + (size_t)i * ld;
+  float ss = 0.f;
+  for (int c = tid; c < q_rank; c += 256) { const float v = to_f(row[c]); ss += v * v; }
+  const float rq = 1.0f / sqrtf(block_sum_256(ss, red) / (float)q_rank + eps);
+  for (int c = tid; c < q_rank; c += 256) cq[(size_t)i * q_rank + c] = from_f<T>(to_f(row[c]) * rq * qn_w[c]);
+  if (!cache) return;
+  const int slot = meta[i], pos = meta[ntok + i];
+  T* crow = cache + ((size_t)slot * cap + (pos % cap)) * (kv_rank + rot_dim);
+  const T* kv = row + q_rank;
+  ss = 0.f;
+  for (int c = tid; c < kv_rank; c += 256) { const float v = to_f(kv[c]); ss += v * v; }
+  const float rk = 1.0f / sqrtf(block_sum_256(ss, red) / (float)kv_rank + eps);
+  for (int c = tid; c < kv_rank; c += 256) crow[c] = from_f<T>(to_f(kv[c]) * rk * kvn_w[c]);
+  const T* kr = kv + kv_rank;
+  const int half = rot_dims >> 1;
+  for (int c = tid; c < half; c += 256) {
+    float sn, cs;
+    sincosf((float)pos * inv_freq[c], &sn, &cs);
+    const float u = to_f(kr[c]), v = to_f(kr[c + half]);
+    crow[kv_rank + c] = from_f<T>(u * cs - v * sn);
+    crow[kv_rank + c + half] = from_f<T>(v * cs + u * sn);
+  }
+  for (int c = rot_dims + tid; c < rot_dim; c += 256) crow[kv_rank + c] = kr[c];
+}
+
+// Rotary positions on a slice of every head: dst[t, h, 0:n] = rotate(src[t, h, off : off + n]) in float32, the first
+// rot_dims entries rotated (entry i paired with i + rot_dims / 2), the rest copied.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rotary_kernel(const T* __restrict__ src, long long src_ts, int src_hs, int off, float* __restrict__ dst, long long dst_ts, int dst_hs,
+              int H, int n, int rot_dims, const float* __restrict__ inv_freq, const int* __restrict__ meta, int ntok) {
+  pdl_enter();
+  const int i = blockIdx.x;
+  const int pos = meta[ntok + i];
+  const int half = rot_dims >> 1, rest = n - rot_dims, per = half + rest;
+  for (int k = threadIdx.x; k < H * per; k += 128) {
+    const int h = k / per, c = k % per;
+    const T* s = src + (size_t)i * src_ts + (size_t)h * src_hs + off;
+    float* o = dst + (size_t)i * dst_ts + (size_t)h * dst_hs;
+    if (c < half) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[c], &sn, &cs);
+      const float u = to_f(s[c]), v = to_f(s[c + half]);
+      o[c] = u * cs - v * sn;
+      o[c + half] = v * cs + u * sn;
+    } else {
+      o[rot_dims + c - half] = to_f(s[rot_dims + c - half]);
+    }
+  }
+}
+
+// ---- grouped-query attention: norm over the whole query / key projection, cache write -----------------------------
+// Row of p: [q (HD) | k (GD) | v (GDV) | ...], biases already added by the projection. q -> float32 buffer, k and v ->
+// ring cache rows (position % cap).
+template <typename T>
+__global__ void __launch_bounds__(256)
+qkv_prep_kernel(const T* __restrict__ p, int ld, int HD, int GD, int GDV, const float* __restrict__ qn_w,
+                const float* __restrict__ kn_w, float* __restrict__ qout, T* __restrict__ cache_k, T* __restrict__ cache_v, int cap,
+                const int* __restrict__ meta, int ntok, float eps) {
+  pdl_enter();
+  __shared__ float red[8];
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const T* row = p + (size_t)i * ld;
+  const int slot = meta[i], pos = meta[ntok + i];
+  float ss = 0.f;
+  for (int c = tid; c < HD; c += 256) { const float v = to_f(row[c]); ss += v * v; }
+  const float rq = 1.0f / sqrtf(block_sum_256(ss, red) / (float)HD + eps);
+  for (int c = tid; c < HD; c += 256) qout[(size_t)i * HD + c] = to_f(row[c]) * rq * qn_w[c];
+  const T* k = row + HD;
+  ss = 0.f;
+  for (int c = tid; c < GD; c += 256) { const float v = to_f(k[c]); ss += v * v; }
+  const float rk = 1.0f / sqrtf(block_sum_256(ss, red) / (float)GD + eps);
+  const size_t r = (size_t)slot * cap + (pos % cap);
+  for (int c = tid; c < GD; c += 256) cache_k[r * GD + c] = from_f<T>(to_f(k[c]) * rk * kn_w[c]);
+  const T* v = k + GD;
+  for (int c = tid; c < GDV; c += 256) cache_v[r * GDV + c] = v[c];
+}
+
+// ---- sliding-window softmax attention with a sink -------------------------------------------------------------------
+// One CTA of four warps per (token, query head). Query = two float32 parts (qa against key[0:DA], qb against
+// key[DA:DA+DB]); keys and values are rows of a per-slot ring (row = position % cap) that already holds the step's
+// own tokens. A warp takes every fourth key of the window: lanes along the row for the dot product, an online softmax
+// per warp, and the four partial results are merged in shared memory together with the sink term exp(sink[h]) of the
+// denominator. Which warp takes which key depends on the token's position only, so a token's result does not depend
+// on how its sequence was cut into steps or on its neighbours in the batch.
+template <typename T, int NACC, int VEC>
+__global__ void __launch_bounds__(128)
+window_attn_kernel(const float* __restrict__ qa, long long qa_ts, long long qa_hs, int DA, const float* __restrict__ qb,
+                   long long qb_ts, long long qb_hs, int DB, const T* __restrict__ kc, long long k_ss, int k_rs, int k_hs,
+                   const T* __restrict__ vc, long long v_ss, int v_rs, int v_hs, int DV, const float* __restrict__ sink,
+                   const T* __restrict__ gate, int gate_ld, T* __restrict__ out, const int* __restrict__ meta, int ntok, int H,
+                   int G, int window, int cap, float scale) {
+  pdl_enter();
+  extern __shared__ float sm_wa[];            // q [DK] | acc [4][DV]
+  __shared__ float s_m[4], s_l[4];
+  const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int DK = DA + DB;
+  float* sq = sm_wa;
+  float* sacc = sm_wa + ((DK + 3) & ~3);
+  const int slot = meta[i], pos = meta[ntok + i];
+  const int g = h / (H / G);
+  for (int c = tid; c < DA; c += 128) sq[c] = qa[(size_t)i * qa_ts + (size_t)h * qa_hs + c];
+  for (int c = tid; c < DB; c += 128) sq[DA + c] = qb[(size_t)i * qb_ts + (size_t)h * qb_hs + c];
+  __syncthreads();
+  const T* kbase = kc + (size_t)slot * k_ss + (size_t)g * k_hs;
+  const T* vbase = vc + (size_t)slot * v_ss + (size_t)g * v_hs;
+  const int j0 = max(0, pos - window + 1);
+  float m = -INFINITY, l = 0.f;
+  float acc[NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
+  for (int j = j0 + warp; j <= pos; j += 4) {
+    const int r = j % cap;
+    const T* kr = kbase + (size_t)r * k_rs;
+    float dot = 0.f;
+    for (int c = lane * VEC; c < DK; c += 32 * VEC) {
+      float kv[2];
+      ld_pair<VEC>(kr + c, kv);
+      dot += sq[c] * kv[0];
+      if (VEC == 2) dot += sq[c + 1] * kv[1];
+    }
+    const float s = warp_xor_sum(dot) * scale;
+    const float mn = fmaxf(m, s);
+    const float corr = expf(m - mn), p = expf(s - mn);
+    m = mn;
+    l = l * corr + p;
+    const T* vr = vbase + (size_t)r * v_rs;
+#pragma unroll
+    for (int a = 0; a < NACC; a += VEC) {
+      const int c = lane * VEC + 32 * a;
+      float vv[2] = {0.f, 0.f};
+      if (c < DV) ld_pair<VEC>(vr + c, vv);
+      acc[a] = acc[a] * corr + p * vv[0];
+      if (VEC == 2) acc[a + 1] = acc[a + 1] * corr + p * vv[1];
+    }
+  }
+  if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+  for (int a = 0; a < NACC; a += VEC) {
+    const int c = lane * VEC + 32 * a;
+    if (c < DV) {
+      sacc[warp * DV + c] = acc[a];
+      if (VEC == 2) sacc[warp * DV + c + 1] = acc[a + 1];
+    }
+  }
+  __syncthreads();
+  float M = sink ? sink[h] : -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) M = fmaxf(M, s_m[w]);
+  float f[4], L = sink ? expf(sink[h] - M) : 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    f[w] = expf(s_m[w] - M);               // a warp without keys has m = -inf: factor 0
+    L += s_l[w] * f[w];
+  }
+  const float inv = 1.0f / L;
+  for (int c = tid; c < DV; c += 128) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) o += sacc[w * DV + c] * f[w];
+    o *= inv;
+    if (gate) o *= 1.0f / (1.0f + expf(-to_f(gate[(size_t)i * gate_ld + (size_t)h * DV + c])));
+    out[((size_t)i * H + h) * DV + c] = from_f<T>(o);
+  }
+}
+
+// ---- HGRN2: gated linear recurrence ---------------------------------------------------------------------------------
+// Per head S <- diag(f) S + (1 - f) v^T, o = S^T q with f = lower + (1 - lower) sigmoid(zf + b) and q = silu(zq).
+// One CTA per (segment, head, slice of 32 value columns) walks the segment's tokens in order, eight at a time; thread
+// (warp w, lane) keeps rows w * NS .. of column `lane` of the state in registers (float32). For a block of eight tokens
+// the gates, queries and values are computed once into shared memory (their raw projections were fetched into registers
+// while the previous block was applied), then every warp applies the eight tokens to its rows, and the eight warps'
+// partial outputs are added, one token per warp. The state is loaded from the slot at the start (zero at position 0)
+// and stored at the end. o leaves un-normalised, float32.
+template <typename T, int NS>
+__global__ void __launch_bounds__(256)
+hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b, const float* __restrict__ lower,
+                  float* __restrict__ state, float* __restrict__ o, const int* __restrict__ meta, int ntok, int H, int D, int DV) {
+  pdl_enter();
+  const int i = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
+  const TokMeta mt = load_meta(meta, ntok, i);
+  if (i != mt.seg_begin) return;
+  constexpr int BT = 8, DP = 8 * NS, R = (BT * DP) / 256;      // tokens per block, padded rows, staged values per thread
+  __shared__ float sq[BT][DP], sf[BT][DP], sg[BT][DP], sv[BT][32], spart[BT][8][32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int col = v0 + lane;
+  const bool live = col < DV;
+  const int d0 = warp * NS;
+  float S[NS];
+  float* st = state + (((size_t)mt.slot * H + h) * D) * DV;
+#pragma unroll
+  for (int k = 0; k < NS; ++k) S[k] = (mt.pos > 0 && live && d0 + k < D) ? st[(size_t)(d0 + k) * DV + col] : 0.f;
+  const int HD = H * D;
+  float zq[R], zf[R], zv;
+  auto fetch = [&](int tb) {                               // raw projections of tokens tb .. tb + 7 into registers
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int e = tid + 256 * r, tt = e / DP, d = e % DP, t = tb + tt;
+      zq[r] = 0.f; zf[r] = 0.f;
+      if (t < mt.seg_end && d < D) {
+        const T* row = p + (size_t)t * ld + h * D + d;
+        zq[r] = to_f(row[0]);
+        zf[r] = to_f(row[HD]);
+      }
+    }
+    const int t = tb + warp;
+    zv = (t < mt.seg_end && live) ? to_f(p[(size_t)t * ld + 2 * HD + h * DV + col]) : 0.f;
+  };
+  fetch(mt.seg_begin);
+  for (int tb = mt.seg_begin; tb < mt.seg_end; tb += BT) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int e = tid + 256 * r, tt = e / DP, d = e % DP;
+      float q = 0.f, f = 1.f, gq = 0.f;
+      if (d < D) {
+        const float lo = lower[h * D + d], z = zf[r] + f_b[h * D + d];
+        q = zq[r] / (1.0f + expf(-zq[r]));
+        const float om = 1.0f / (1.0f + expf(z));           // 1 - sigmoid(z)
+        gq = (1.0f - lo) * om;                              // 1 - f
+        f = lo + (1.0f - lo) * (1.0f - om);
+      }
+      sq[tt][d] = q; sf[tt][d] = f; sg[tt][d] = gq;
+    }
+    sv[warp][lane] = zv;
+    __syncthreads();
+    if (tb + BT < mt.seg_end) fetch(tb + BT);
+    const int nb = min(BT, mt.seg_end - tb);
+    for (int tt = 0; tt < nb; ++tt) {
+      const float v = sv[tt][lane];
+      float part = 0.f;
+#pragma unroll
+      for (int k = 0; k < NS; ++k) {
+        S[k] = sf[tt][d0 + k] * S[k] + sg[tt][d0 + k] * v;
+        part += S[k] * sq[tt][d0 + k];
+      }
+      spart[tt][warp][lane] = part;
+    }
+    __syncthreads();
+    if (warp < nb && live) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) s += spart[warp][w][lane];
+      o[(size_t)(tb + warp) * H * DV + (size_t)h * DV + col] = s;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int k = 0; k < NS; ++k)
+      if (d0 + k < D) st[(size_t)(d0 + k) * DV + col] = S[k];
+  }
+}
+
+// Per-head unit-RMS norm with one weight vector shared by the heads: one warp per (token, head); src float32.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_kernel(const float* __restrict__ src, const float* __restrict__ w, T* __restrict__ out, long long rows, int DV, float eps) {
+  pdl_enter();
+  const long long r = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* s = src + r * DV;
+  float ss = 0.f;
+  for (int c = lane; c < DV; c += 32) ss += s[c] * s[c];
+  const float rr = 1.0f / sqrtf(warp_xor_sum(ss) / (float)DV + eps);
+  for (int c = lane; c < DV; c += 32) out[r * DV + c] = from_f<T>(s[c] * rr * w[c]);
+}
+
+// ---- per-token side input: g <- gelu_tanh(g) * table[id, layer part] -------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+side_gate_kernel(T* __restrict__ g, const T* __restrict__ table, const int* __restrict__ ids, int col0, int sd, int table_ld, int V,
+                 long long n) {
+  pdl_enter();
+  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
+    const long long t = k / sd;
+    const int c = (int)(k % sd);
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const float z = to_f(g[k]);
+    const float ge = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    g[k] = from_f<T>(ge * to_f(table[(size_t)id * table_ld + col0 + c]));
+  }
+}
+
+}  // namespace qspec
+
+using namespace qspec;
+
+#define MIX_DTYPE_OK(dtype) QSPEC_REQUIRE((dtype) == QSPEC_DTYPE_BF16 || (dtype) == QSPEC_DTYPE_F32, QSPEC_ERR_UNSUPPORTED, \
+                                          "dtype %d: bfloat16 (1) or float32 (2) expected", (dtype))
+typedef __nv_bfloat16 bf16_t;
+
+extern "C" int qspec_seq_token_shift(const float* x, const float* shift, float* prev, int slots, void* out, const int* meta,
+                                     int ntok, int W, int dtype, void* stream) {
+  QSPEC_REQUIRE(x && shift && prev && out && meta, QSPEC_ERR_INVALID_ARG, "seq_token_shift: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && slots > 0, QSPEC_ERR_INVALID_ARG, "seq_token_shift: bad sizes");
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(token_shift_kernel<float>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, x, shift, prev, slots, (float*)out, meta, ntok, W);
+  else
+    launch_pdl(token_shift_kernel<bf16_t>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, x, shift, prev, slots, (bf16_t*)out, meta, ntok, W);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+template <typename T, typename YT>
+static int launch_add_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride, long long y_tok_stride,
+                           const float* y_w, const float* w, const float* b, int kind, void* out, int ntok, int W, float eps,
+                           cudaStream_t st) {
+  const size_t smem = (size_t)W * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(add_norm_kernel<T, YT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  launch_pdl(add_norm_kernel<T, YT>, dim3(ntok), dim3(256), smem, st, x_in, x_out, (const YT*)y, y_parts, y_part_stride, y_tok_stride,
+             y_w, w, b, kind, (T*)out, W, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_add_norm(const float* x_in, float* x_out, const void* y, int y_parts, long long y_part_stride,
+                                  long long y_tok_stride, const float* y_w, const float* w, const float* b, int kind, void* out,
+                                  int ntok, int W, float eps, int y_dtype, int dtype, void* stream) {
+  QSPEC_REQUIRE(y && w && (x_out || out), QSPEC_ERR_INVALID_ARG, "seq_add_norm: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && W > 0 && W <= 49152 && y_parts >= 1 && (kind == 0 || kind == 1), QSPEC_ERR_INVALID_ARG,
+                "seq_add_norm: bad sizes (width <= 49152, kind 0 or 1)");
+  MIX_DTYPE_OK(dtype);
+  QSPEC_REQUIRE(y_dtype == dtype || y_dtype == QSPEC_DTYPE_F32, QSPEC_ERR_UNSUPPORTED, "seq_add_norm: y is of the activation type or float32");
+  if (ntok == 0) return QSPEC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+#define AN_ARGS x_in, x_out, y, y_parts, y_part_stride, y_tok_stride, y_w, w, b, kind, out, ntok, W, eps, st
+  if (dtype == QSPEC_DTYPE_F32) return launch_add_norm<float, float>(AN_ARGS);
+  if (y_dtype == QSPEC_DTYPE_F32) return launch_add_norm<bf16_t, float>(AN_ARGS);
+  return launch_add_norm<bf16_t, bf16_t>(AN_ARGS);
+#undef AN_ARGS
+}
+
+extern "C" int qspec_seq_latent_prep(const void* d, int ld, int q_rank, int kv_rank, int rot_dim, const float* qn_w, const float* kvn_w,
+                                     const float* inv_freq, int rot_dims, void* cq, void* cache, int cap, const int* meta, int ntok,
+                                     float eps, int dtype, void* stream) {
+  QSPEC_REQUIRE(d && qn_w && cq && meta, QSPEC_ERR_INVALID_ARG, "seq_latent_prep: null pointer");
+  QSPEC_REQUIRE(!cache || (kvn_w && inv_freq), QSPEC_ERR_INVALID_ARG, "seq_latent_prep: a cache needs the key/value norm weight and the frequencies");
+  QSPEC_REQUIRE(ntok >= 0 && q_rank > 0 && kv_rank >= 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 &&
+                    cap > 0 && ld >= q_rank + (cache ? kv_rank + rot_dim : 0),
+                QSPEC_ERR_INVALID_ARG, "seq_latent_prep: bad sizes");
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(latent_prep_kernel<float>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const float*)d, ld, q_rank, kv_rank, rot_dim,
+               qn_w, kvn_w, inv_freq, rot_dims, (float*)cq, (float*)cache, cap, meta, ntok, eps);
+  else
+    launch_pdl(latent_prep_kernel<bf16_t>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const bf16_t*)d, ld, q_rank, kv_rank, rot_dim,
+               qn_w, kvn_w, inv_freq, rot_dims, (bf16_t*)cq, (bf16_t*)cache, cap, meta, ntok, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_rotary(const void* src, long long src_ts, int src_hs, int off, float* dst, long long dst_ts, int dst_hs, int H,
+                                int n, int rot_dims, const float* inv_freq, const int* meta, int ntok, int dtype, void* stream) {
+  QSPEC_REQUIRE(src && dst && meta && (rot_dims == 0 || inv_freq), QSPEC_ERR_INVALID_ARG, "seq_rotary: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && H > 0 && n >= 0 && rot_dims >= 0 && rot_dims <= n && rot_dims % 2 == 0, QSPEC_ERR_INVALID_ARG,
+                "seq_rotary: bad sizes");
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0 || n == 0) return QSPEC_OK;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(rotary_kernel<float>, dim3(ntok), dim3(128), 0, (cudaStream_t)stream, (const float*)src, src_ts, src_hs, off, dst, dst_ts,
+               dst_hs, H, n, rot_dims, inv_freq, meta, ntok);
+  else
+    launch_pdl(rotary_kernel<bf16_t>, dim3(ntok), dim3(128), 0, (cudaStream_t)stream, (const bf16_t*)src, src_ts, src_hs, off, dst, dst_ts,
+               dst_hs, H, n, rot_dims, inv_freq, meta, ntok);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_qkv_prep(const void* p, int ld, int HD, int GD, int GDV, const float* qn_w, const float* kn_w, float* qout,
+                                  void* cache_k, void* cache_v, int cap, const int* meta, int ntok, float eps, int dtype, void* stream) {
+  QSPEC_REQUIRE(p && qn_w && kn_w && qout && cache_k && cache_v && meta, QSPEC_ERR_INVALID_ARG, "seq_qkv_prep: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && HD > 0 && GD > 0 && GDV > 0 && cap > 0 && ld >= HD + GD + GDV, QSPEC_ERR_INVALID_ARG, "seq_qkv_prep: bad sizes");
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(qkv_prep_kernel<float>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const float*)p, ld, HD, GD, GDV, qn_w, kn_w, qout,
+               (float*)cache_k, (float*)cache_v, cap, meta, ntok, eps);
+  else
+    launch_pdl(qkv_prep_kernel<bf16_t>, dim3(ntok), dim3(256), 0, (cudaStream_t)stream, (const bf16_t*)p, ld, HD, GD, GDV, qn_w, kn_w, qout,
+               (bf16_t*)cache_k, (bf16_t*)cache_v, cap, meta, ntok, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+template <typename T, int NACC, int VEC>
+static int launch_window_attn(const qspec_window_attn_args* a, cudaStream_t st) {
+  const int DK = a->DA + a->DB;
+  const size_t smem = ((size_t)((DK + 3) & ~3) + (size_t)4 * a->DV) * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(window_attn_kernel<T, NACC, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  launch_pdl(window_attn_kernel<T, NACC, VEC>, dim3(a->ntok, a->H), dim3(128), smem, st, a->qa, a->qa_tok_stride, a->qa_head_stride, a->DA,
+             a->qb, a->qb_tok_stride, a->qb_head_stride, a->DB, (const T*)a->k, a->k_slot_stride, a->k_row_stride, a->k_head_stride,
+             (const T*)a->v, a->v_slot_stride, a->v_row_stride, a->v_head_stride, a->DV, a->sink, (const T*)a->gate, a->gate_ld, (T*)a->out,
+             a->meta, a->ntok, a->H, a->G, a->window, a->cap, a->scale);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+template <typename T, int VEC>
+static int launch_window_attn_n(const qspec_window_attn_args* a, cudaStream_t st) {
+  const int per = (a->DV + 31) / 32;
+  if (per <= 2) return launch_window_attn<T, 2, VEC>(a, st);
+  if (per <= 4) return launch_window_attn<T, 4, VEC>(a, st);
+  if (per <= 8) return launch_window_attn<T, 8, VEC>(a, st);
+  return launch_window_attn<T, 16, VEC>(a, st);
+}
+
+extern "C" int qspec_seq_window_attention(const qspec_window_attn_args* a, int dtype, void* stream) {
+  QSPEC_REQUIRE(a && a->qa && a->k && a->v && a->out && a->meta && (a->DB == 0 || a->qb), QSPEC_ERR_INVALID_ARG,
+                "seq_window_attention: null pointer");
+  QSPEC_REQUIRE(a->ntok >= 0 && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->DA > 0 && a->DB >= 0 && a->DV > 0 && a->DV <= 512 &&
+                    a->DA + a->DB <= 8192 && a->window >= 1 && a->cap >= 1 && a->H <= 65535,
+                QSPEC_ERR_UNSUPPORTED, "seq_window_attention: heads %d / %d, key size %d + %d (<= 8192), value size %d (<= 512)", a->H,
+                a->G, a->DA, a->DB, a->DV);
+  MIX_DTYPE_OK(dtype);
+  if (a->ntok == 0) return QSPEC_OK;
+  const size_t esz = dtype == QSPEC_DTYPE_F32 ? 4 : 2;
+  const bool even = ((a->DA + a->DB) % 2 == 0) && (a->DV % 2 == 0) && (a->k_row_stride % 2 == 0) && (a->k_head_stride % 2 == 0) &&
+                    (a->k_slot_stride % 2 == 0) && (a->v_row_stride % 2 == 0) && (a->v_head_stride % 2 == 0) && (a->v_slot_stride % 2 == 0) &&
+                    ((uintptr_t)a->k % (2 * esz) == 0) && ((uintptr_t)a->v % (2 * esz) == 0);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == QSPEC_DTYPE_F32) return even ? launch_window_attn_n<float, 2>(a, st) : launch_window_attn_n<float, 1>(a, st);
+  return even ? launch_window_attn_n<bf16_t, 2>(a, st) : launch_window_attn_n<bf16_t, 1>(a, st);
+}
+
+template <typename T>
+static int launch_hgrn2(const void* p, int ld, const float* f_b, const float* lower, float* state, float* o, const int* meta, int ntok,
+                        int H, int D, int DV, cudaStream_t st) {
+  const dim3 grid(ntok, H, (DV + 31) / 32);
+#define HG_ARGS dim3(256), 0, st, (const T*)p, ld, f_b, lower, state, o, meta, ntok, H, D, DV
+  if (D <= 32) launch_pdl(hgrn2_scan_kernel<T, 4>, grid, HG_ARGS);
+  else if (D <= 64) launch_pdl(hgrn2_scan_kernel<T, 8>, grid, HG_ARGS);
+  else if (D <= 128) launch_pdl(hgrn2_scan_kernel<T, 16>, grid, HG_ARGS);
+  else launch_pdl(hgrn2_scan_kernel<T, 32>, grid, HG_ARGS);
+#undef HG_ARGS
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_hgrn2(const void* p, int ld, const float* f_b, const float* lower, const float* norm_w, float* state,
+                               float* scratch, void* out, const int* meta, int ntok, int H, int D, int DV, float eps, int dtype,
+                               void* stream) {
+  QSPEC_REQUIRE(p && f_b && lower && norm_w && state && scratch && out && meta, QSPEC_ERR_INVALID_ARG, "seq_hgrn2: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && H > 0 && H <= 65535 && D > 0 && D <= 256 && DV > 0 && DV <= 65535 * 32 && ld >= 2 * H * D + H * DV,
+                QSPEC_ERR_UNSUPPORTED, "seq_hgrn2: %d heads, key size %d (<= 256), value size %d", H, D, DV);
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  int s = dtype == QSPEC_DTYPE_F32 ? launch_hgrn2<float>(p, ld, f_b, lower, state, scratch, meta, ntok, H, D, DV, st)
+                                   : launch_hgrn2<bf16_t>(p, ld, f_b, lower, state, scratch, meta, ntok, H, D, DV, st);
+  if (s) return s;
+  const long long rows = (long long)ntok * H;
+  const unsigned blocks = (unsigned)((rows + 3) / 4);
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(head_norm_kernel<float>, dim3(blocks), dim3(128), 0, st, (const float*)scratch, norm_w, (float*)out, rows, DV, eps);
+  else
+    launch_pdl(head_norm_kernel<bf16_t>, dim3(blocks), dim3(128), 0, st, (const float*)scratch, norm_w, (bf16_t*)out, rows, DV, eps);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+extern "C" int qspec_seq_side_gate(void* g, const void* table, const int* ids, int col0, int sd, int table_ld, int V, int ntok, int dtype,
+                                   void* stream) {
+  QSPEC_REQUIRE(g && table && ids, QSPEC_ERR_INVALID_ARG, "seq_side_gate: null pointer");
+  QSPEC_REQUIRE(ntok >= 0 && sd > 0 && col0 >= 0 && col0 + sd <= table_ld && V > 0, QSPEC_ERR_INVALID_ARG, "seq_side_gate: bad sizes");
+  MIX_DTYPE_OK(dtype);
+  if (ntok == 0) return QSPEC_OK;
+  const long long n = (long long)ntok * sd;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == QSPEC_DTYPE_F32)
+    launch_pdl(side_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (float*)g, (const float*)table, ids, col0,
+               sd, table_ld, V, n);
+  else
+    launch_pdl(side_gate_kernel<bf16_t>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (bf16_t*)g, (const bf16_t*)table, ids,
+               col0, sd, table_ld, V, n);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}

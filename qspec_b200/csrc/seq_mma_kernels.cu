@@ -688,7 +688,9 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
-template <bool DUAL>
+// MODE 0: down product (rows in sorted order, output scattered to [token, choice]); 1: [gate ; up] product with the clamped
+// gated activation; 2: up product alone with the squared-ReLU activation (rows gathered, output in sorted order).
+template <int MODE>
 __global__ void __launch_bounds__(256)
 grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, bf16* __restrict__ C, GroupPlan p, int K, int N, int top,
                        float limit) {
@@ -704,6 +706,7 @@ grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, b
   const uint32_t base = (tc_smem_u32(tc_smem_raw) + 1023u) & ~1023u;      // stage s: A at base + s * 32 KB, B 16 KB after it
   const int e = p.tile_expert[tile], m0 = p.tile_row0[tile];
   const int mend = p.offsets[e + 1];
+  constexpr bool DUAL = MODE == 1, GATHER = MODE != 0;
   constexpr int BN = DUAL ? 64 : 128;                    // output columns per CTA
   const int n0 = blockIdx.y * BN;
   if (tid < GG_BM) {
@@ -734,7 +737,7 @@ grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, b
     const int v = tid + q * 256, r = v / VPR, c8 = v % VPR;
     const int pr = s_row[r];
     a_ok[q] = pr >= 0;
-    a_src[q] = a_ok[q] ? (DUAL ? A + (size_t)(pr / top) * K : A + (size_t)(m0 + r) * K) + c8 * 8 : A;
+    a_src[q] = a_ok[q] ? (GATHER ? A + (size_t)(pr / top) * K : A + (size_t)(m0 + r) * K) + c8 * 8 : A;
     int brow;
     if (DUAL) brow = (r < 64 ? 0 : N) + n0 + (r & 63);
     else brow = n0 + r;
@@ -790,7 +793,7 @@ grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, b
     const int r = (warp & 3) * 32 + lane, half = warp >> 2;
     const int pr = s_row[r];
     const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    bf16* crow = DUAL ? C + (size_t)(m0 + r) * N : C + (size_t)(pr < 0 ? 0 : pr) * N;
+    bf16* crow = GATHER ? C + (size_t)(m0 + r) * N : C + (size_t)(pr < 0 ? 0 : pr) * N;
     constexpr int GROUPS = DUAL ? 2 : 4;                 // groups of 16 output columns per warp
 #pragma unroll
     for (int gq = 0; gq < GROUPS; ++gq) {
@@ -807,6 +810,9 @@ grouped_gemm_tc_kernel(const bf16* __restrict__ A, const bf16* __restrict__ B, b
           const float gv = fminf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(a[x]))), limit);
           const float uv = fminf(fmaxf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(b[x]))), -limit), limit);
           v[x] = gv * (1.0f / (1.0f + expf(-1.702f * gv))) * (uv + 1.0f);
+        } else if (MODE == 2) {
+          const float u = fmaxf(__bfloat162float(__float2bfloat16_rn(__uint_as_float(a[x]))), 0.f);
+          v[x] = u * u;
         } else {
           v[x] = __uint_as_float(a[x]);
         }
@@ -879,9 +885,10 @@ extern "C" size_t qspec_moe_grouped_workspace_bytes(int ntok, int top, int E, in
   return grouped_layout(ntok > 0 ? ntok : 0, top, E, F, off);
 }
 
-extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
-                                        int W, int F, int E, int top, float limit, void* workspace, size_t workspace_bytes,
-                                        void* stream) {
+extern "C" int qspec_moe_expert_grouped_act(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
+                                            int W, int F, int E, int top, float limit, int act, void* workspace,
+                                            size_t workspace_bytes, void* stream) {
+  QSPEC_REQUIRE(act == QSPEC_EXPERT_ACT_GATED || act == QSPEC_EXPERT_ACT_RELU2, QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: unknown activation %d", act);
   QSPEC_REQUIRE(h && idx && out && workspace && (E == 0 || (gate_up && down)), QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: null pointer");
   QSPEC_REQUIRE(ntok >= 0 && top >= 1 && E >= 0 && E <= 8192, QSPEC_ERR_INVALID_ARG, "moe_expert_grouped: bad sizes");
   QSPEC_REQUIRE(qspec_moe_expert_grouped_supported(W, F), QSPEC_ERR_UNSUPPORTED,
@@ -908,17 +915,24 @@ extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, cons
   if (!configured) {
     QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
     QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GG_SMEM));
-    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
-    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+    QSPEC_CUDA(cudaFuncSetAttribute(grouped_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
     configured = true;
   }
   // QSPEC_SEQ_GROUPED=mma selects the warp-level (mma.sync) tiles, kept as the comparison form for timing and tests
   static const bool warp_level = [] { const char* v = getenv("QSPEC_SEQ_GROUPED"); return v && !strcmp(v, "mma"); }();
+  QSPEC_REQUIRE(!warp_level || act == QSPEC_EXPERT_ACT_GATED, QSPEC_ERR_UNSUPPORTED,
+                "moe_expert_grouped: the warp-level comparison form has the gated activation only");
   if (!warp_level) {
-    launch_pdl(grouped_gemm_tc_kernel<true>, dim3(max_tiles, (F + 63) / 64), dim3(256), TC_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y,
-               p, W, F, top, limit);
+    if (act == QSPEC_EXPERT_ACT_RELU2)
+      launch_pdl(grouped_gemm_tc_kernel<2>, dim3(max_tiles, (F + 127) / 128), dim3(256), TC_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y,
+                 p, W, F, top, limit);
+    else
+      launch_pdl(grouped_gemm_tc_kernel<1>, dim3(max_tiles, (F + 63) / 64), dim3(256), TC_SMEM, st, (const bf16*)h, (const bf16*)gate_up, Y,
+                 p, W, F, top, limit);
     QSPEC_CHECK_LAUNCH(1);
-    launch_pdl(grouped_gemm_tc_kernel<false>, dim3(max_tiles, (W + 127) / 128), dim3(256), TC_SMEM, st, (const bf16*)Y, (const bf16*)down,
+    launch_pdl(grouped_gemm_tc_kernel<0>, dim3(max_tiles, (W + 127) / 128), dim3(256), TC_SMEM, st, (const bf16*)Y, (const bf16*)down,
                (bf16*)out, p, F, W, top, limit);
     QSPEC_CHECK_LAUNCH(1);
     return QSPEC_OK;
@@ -930,4 +944,11 @@ extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, cons
              p, F, W, top, limit);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
+}
+
+extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, const void* down, const int* idx, void* out, int ntok,
+                                        int W, int F, int E, int top, float limit, void* workspace, size_t workspace_bytes,
+                                        void* stream) {
+  return qspec_moe_expert_grouped_act(h, gate_up, down, idx, out, ntok, W, F, E, top, limit, QSPEC_EXPERT_ACT_GATED, workspace,
+                                      workspace_bytes, stream);
 }

@@ -870,17 +870,23 @@ def moe_route(h: torch.Tensor, router_w: torch.Tensor, correction: torch.Tensor,
                                          _stream()), "moe_route")
 
 
+EXPERT_ACTS = {"gated": 0, "relu2": 1}       # QSPEC_EXPERT_ACT_* of include/qspec_b200_seq.h
+
+
 def moe_expert_tokens(h: torch.Tensor, gate_up: Optional[torch.Tensor], down: Optional[torch.Tensor], idx: torch.Tensor,
-                      out: torch.Tensor, E: int, F: int, limit: float) -> None:
-    """Expert outputs per (token, choice), unweighted: out [ntok, top, W]; choices >= E copy h (identity experts)."""
+                      out: torch.Tensor, E: int, F: int, limit: float, act: str = "gated") -> None:
+    """Expert outputs per (token, choice), unweighted: out [ntok, top, W]; choices >= E copy h (identity experts).
+    act "gated": gate_up [E, 2F, W], the clamped gated activation; "relu2": gate_up is the up matrix [E, F, W] alone and
+    the activation is the squared ReLU (limit unused)."""
     _chk(h, "h", _SEQ_ACT); _chk(out, "out", (h.dtype,)); _chk(idx, "idx", (torch.int32,))
     _chk(gate_up, "gate_up", (h.dtype,), allow_none=E == 0); _chk(down, "down", (h.dtype,), allow_none=E == 0)
     ntok, W = h.shape
     top = idx.shape[1]
-    if out.shape != (ntok, top, W) or (E and (gate_up.shape != (E, 2 * F, W) or down.shape != (E, W, F))):
+    rows = F if act == "relu2" else 2 * F
+    if out.shape != (ntok, top, W) or (E and (gate_up.shape != (E, rows, W) or down.shape != (E, W, F))):
         raise ValueError("moe_expert_tokens: shapes do not match")
-    _seq(_lib.load_seq().qspec_moe_expert_tokens(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top,
-                                                 float(limit), _sdt(h), _stream()), "moe_expert_tokens")
+    _seq(_lib.load_seq().qspec_moe_expert_tokens_act(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top,
+                                                     float(limit), EXPERT_ACTS[act], _sdt(h), _stream()), "moe_expert_tokens")
 
 
 def moe_grouped_status(device="cuda") -> int:
@@ -896,16 +902,156 @@ def moe_expert_grouped_supported(h: torch.Tensor, F: int) -> bool:
 
 
 def moe_expert_grouped(h: torch.Tensor, gate_up: Optional[torch.Tensor], down: Optional[torch.Tensor], idx: torch.Tensor,
-                       out: torch.Tensor, E: int, F: int, limit: float) -> None:
+                       out: torch.Tensor, E: int, F: int, limit: float, act: str = "gated") -> None:
     """`moe_expert_tokens` for many tokens (bfloat16): the (token, choice) pairs are sorted by expert and every expert's rows
     go through tensor-core tiles; same outputs up to the summation order."""
     _chk(h, "h", (_BF16,)); _chk(out, "out", (_BF16,)); _chk(idx, "idx", (torch.int32,))
     _chk(gate_up, "gate_up", (_BF16,), allow_none=E == 0); _chk(down, "down", (_BF16,), allow_none=E == 0)
     ntok, W = h.shape
     top = idx.shape[1]
-    if out.shape != (ntok, top, W) or (E and (gate_up.shape != (E, 2 * F, W) or down.shape != (E, W, F))):
+    rows = F if act == "relu2" else 2 * F
+    if out.shape != (ntok, top, W) or (E and (gate_up.shape != (E, rows, W) or down.shape != (E, W, F))):
         raise ValueError("moe_expert_grouped: shapes do not match")
     lib = _lib.load_seq()
     ws = _workspace("moe_grouped", lib.qspec_moe_grouped_workspace_bytes(ntok, top, E, F), h.device)
-    _seq(lib.qspec_moe_expert_grouped(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top, float(limit),
-                                      _ptr(ws), ws.numel(), _stream()), "moe_expert_grouped")
+    _seq(lib.qspec_moe_expert_grouped_act(_ptr(h), _ptr(gate_up), _ptr(down), _ptr(idx), _ptr(out), ntok, W, F, E, top, float(limit),
+                                          EXPERT_ACTS[act], _ptr(ws), ws.numel(), _stream()), "moe_expert_grouped")
+
+
+def moe_route_chosen(h: torch.Tensor, router_w: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor) -> None:
+    """Router whose weights are a softmax over the chosen logits only: the `top` largest of router_w h (float32)."""
+    _chk(h, "h", _SEQ_ACT); _chk(router_w, "router_w", (_F32,)); _chk(idx, "idx", (torch.int32,)); _chk(weight, "weight", (_F32,))
+    ntok, W = h.shape
+    R, top = router_w.shape[0], idx.shape[1]
+    if router_w.shape[1] != W or idx.shape != (ntok, top) or weight.shape != (ntok, top):
+        raise ValueError("moe_route_chosen: shapes do not match")
+    _seq(_lib.load_seq().qspec_moe_route_chosen(_ptr(h), _ptr(router_w), _ptr(idx), _ptr(weight), ntok, W, R, top, _sdt(h), _stream()),
+         "moe_route_chosen")
+
+
+def seq_token_shift(x: torch.Tensor, shift: torch.Tensor, prev: torch.Tensor, out: torch.Tensor, meta: torch.Tensor) -> None:
+    """out_t = x_t + (x_(t-1) - x_t) * shift; prev float32 [2, slots, W] carries each sequence's last row between steps."""
+    _chk(x, "x", (_F32,)); _chk(shift, "shift", (_F32,)); _chk(prev, "prev", (_F32,)); _chk(out, "out", _SEQ_ACT)
+    _chk(meta, "meta", (torch.int32,))
+    ntok, W = x.shape
+    if out.shape != (ntok, W) or shift.numel() != W or prev.dim() != 3 or prev.shape[0] != 2 or prev.shape[2] != W or meta.shape != (5, ntok):
+        raise ValueError("seq_token_shift: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_token_shift(_ptr(x), _ptr(shift), _ptr(prev), prev.shape[1], _ptr(out), _ptr(meta), ntok, W, _sdt(out),
+                                               _stream()), "seq_token_shift")
+
+
+def seq_add_norm(y: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float, *, kind: str = "layer",
+                 x_in: Optional[torch.Tensor] = None, x_out: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 y_w: Optional[torch.Tensor] = None) -> None:
+    """r = x_in + norm(sum of y's parts) (x_in None: the norm alone); kind "layer": (v - mean) / sqrt(var + eps) * w + b,
+    "rms": v / sqrt(mean(v^2) + eps) * w. y [ntok, W] or [ntok, parts, W] with weights y_w [ntok, parts]. r goes to x_out
+    (float32; may be x_in) and, in out's type, to out."""
+    _chk(w, "w", (_F32,)); _chk(b, "b", (_F32,), allow_none=True); _chk(x_in, "x_in", (_F32,), allow_none=True)
+    _chk(x_out, "x_out", (_F32,), allow_none=True); _chk(out, "out", _SEQ_ACT, allow_none=True); _chk(y_w, "y_w", (_F32,), allow_none=True)
+    _chk(y, "y", _SEQ_ACT)
+    ntok, W = y.shape[0], y.shape[-1]
+    parts, pstride, tstride = (y.shape[1], W, y.shape[1] * W) if y.dim() == 3 else (1, 0, W)
+    for t in (x_in, x_out, out):
+        if t is not None and t.shape != (ntok, W):
+            raise ValueError("seq_add_norm: shapes do not match")
+    if w.numel() != W or (y_w is not None and y_w.shape != (ntok, parts)):
+        raise ValueError("seq_add_norm: shapes do not match")
+    act = _sdt(out) if out is not None else _sdt(y)
+    _seq(_lib.load_seq().qspec_seq_add_norm(_ptr(x_in), _ptr(x_out), _ptr(y), parts, pstride, tstride, _ptr(y_w), _ptr(w), _ptr(b),
+                                            {"layer": 0, "rms": 1}[kind], _ptr(out), ntok, W, float(eps), _sdt(y), act, _stream()),
+         "seq_add_norm")
+
+
+def seq_latent_prep(d: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, qn_w: torch.Tensor, kvn_w: Optional[torch.Tensor],
+                    inv_freq: Optional[torch.Tensor], rot_dims: int, cq: torch.Tensor, cache: Optional[torch.Tensor],
+                    meta: torch.Tensor, eps: float) -> None:
+    """Norms of the low-rank query / key-value projections and the rotary key part; with `cache` [slots, cap, kv_rank + rot_dim]
+    the step's rows are written at position % cap."""
+    _chk(d, "d", _SEQ_ACT); _chk(cq, "cq", (d.dtype,)); _chk(cache, "cache", (d.dtype,), allow_none=True)
+    _chk(qn_w, "qn_w", (_F32,)); _chk(kvn_w, "kvn_w", (_F32,), allow_none=True); _chk(inv_freq, "inv_freq", (_F32,), allow_none=True)
+    ntok = d.shape[0]
+    if cq.shape != (ntok, q_rank) or (cache is not None and cache.shape[2] != kv_rank + rot_dim):
+        raise ValueError("seq_latent_prep: shapes do not match")
+    cap = cache.shape[1] if cache is not None else 1
+    _seq(_lib.load_seq().qspec_seq_latent_prep(_ptr(d), d.shape[1], q_rank, kv_rank, rot_dim, _ptr(qn_w), _ptr(kvn_w), _ptr(inv_freq),
+                                               rot_dims, _ptr(cq), _ptr(cache), cap, _ptr(meta), ntok, float(eps), _sdt(d), _stream()),
+         "seq_latent_prep")
+
+
+def seq_rotary(src: torch.Tensor, off: int, dst: torch.Tensor, rot_dims: int, inv_freq: torch.Tensor, meta: torch.Tensor) -> None:
+    """dst [ntok, H, n] float32 = rotary positions on src[t, h, off : off + n] (src [ntok, H, head size])."""
+    _chk(src, "src", _SEQ_ACT); _chk(dst, "dst", (_F32,)); _chk(inv_freq, "inv_freq", (_F32,))
+    ntok, H, n = dst.shape
+    if src.shape[:2] != (ntok, H) or off + n > src.shape[2]:
+        raise ValueError("seq_rotary: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_rotary(_ptr(src), H * src.shape[2], src.shape[2], off, _ptr(dst), H * n, n, H, n, rot_dims,
+                                          _ptr(inv_freq), _ptr(meta), ntok, _sdt(src), _stream()), "seq_rotary")
+
+
+def seq_qkv_prep(p: torch.Tensor, HD: int, GD: int, GDV: int, qn_w: torch.Tensor, kn_w: torch.Tensor, qout: torch.Tensor,
+                 cache_k: torch.Tensor, cache_v: torch.Tensor, meta: torch.Tensor, eps: float) -> None:
+    """Whole-projection norms of q and k of rows [q | k | v | ...]; q to float32 qout, k and v to their ring caches
+    [slots, cap, GD] / [slots, cap, GDV] at position % cap."""
+    _chk(p, "p", _SEQ_ACT); _chk(qout, "qout", (_F32,)); _chk(cache_k, "cache_k", (p.dtype,)); _chk(cache_v, "cache_v", (p.dtype,))
+    _chk(qn_w, "qn_w", (_F32,)); _chk(kn_w, "kn_w", (_F32,))
+    ntok = p.shape[0]
+    if qout.shape != (ntok, HD) or cache_k.shape[2] != GD or cache_v.shape[2] != GDV or cache_k.shape[:2] != cache_v.shape[:2]:
+        raise ValueError("seq_qkv_prep: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_qkv_prep(_ptr(p), p.shape[1], HD, GD, GDV, _ptr(qn_w), _ptr(kn_w), _ptr(qout), _ptr(cache_k),
+                                            _ptr(cache_v), cache_k.shape[1], _ptr(meta), ntok, float(eps), _sdt(p), _stream()),
+         "seq_qkv_prep")
+
+
+def seq_window_attention(qa: torch.Tensor, qb: Optional[torch.Tensor], cache_k: torch.Tensor, cache_v: torch.Tensor, out: torch.Tensor,
+                         meta: torch.Tensor, window: int, scale: float, sink: Optional[torch.Tensor] = None,
+                         gate: Optional[torch.Tensor] = None) -> None:
+    """Sliding-window softmax attention with a per-head sink over ring caches.
+    qa [ntok, H, DA] and qb [ntok, H, DB] (float32, any strides with a unit last stride): the two parts of the query;
+    cache_k [slots, cap, G, DA + DB], cache_v [slots, cap, G, DV] (views with a unit last stride: a latent cache passes two
+    views of one buffer); out [ntok, H, DV]; gate [ntok, >= H * DV] (sigmoid applied) or None."""
+    import ctypes
+    if qa.dtype != _F32 or (qb is not None and qb.dtype != _F32):
+        raise ValueError("seq_window_attention: queries are float32")
+    if cache_k.dtype != out.dtype or cache_v.dtype != out.dtype or (gate is not None and gate.dtype != out.dtype):
+        raise ValueError("seq_window_attention: caches, gate and out share one element type")
+    _chk(out, "out", _SEQ_ACT)
+    ntok, H, DA = qa.shape
+    DB = qb.shape[2] if qb is not None else 0
+    slots, cap, G, DK = cache_k.shape
+    DV = cache_v.shape[3]
+    if DK != DA + DB or out.shape != (ntok, H, DV) or cache_v.shape[:3] != (slots, cap, G) or meta.shape != (5, ntok):
+        raise ValueError("seq_window_attention: shapes do not match")
+    for t in (qa, qb, cache_k, cache_v):
+        if t is not None and t.stride(-1) != 1:
+            raise ValueError("seq_window_attention: the last stride must be 1")
+    a = _lib.WindowAttnArgs(qa.data_ptr(), qa.stride(0), qa.stride(1), DA,
+                            qb.data_ptr() if qb is not None else None, qb.stride(0) if qb is not None else 0,
+                            qb.stride(1) if qb is not None else 0, DB,
+                            cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1), cache_k.stride(2),
+                            cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1), cache_v.stride(2), DV,
+                            _ptr(sink), gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
+                            _ptr(out), _ptr(meta), ntok, H, G, int(window), cap, float(scale))
+    _seq(_lib.load_seq().qspec_seq_window_attention(ctypes.byref(a), _sdt(out), _stream()), "seq_window_attention")
+
+
+def seq_hgrn2(p: torch.Tensor, f_b: torch.Tensor, lower: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, scratch: torch.Tensor,
+              out: torch.Tensor, meta: torch.Tensor, H: int, D: int, DV: int, eps: float) -> None:
+    """HGRN2 recurrence over rows [zq | zf | v] with the per-slot state float32 [slots, H, D, DV]; out [ntok, H * DV] after the
+    per-head norm; scratch float32 with room for [ntok, H * DV]."""
+    _chk(p, "p", _SEQ_ACT); _chk(out, "out", (p.dtype,)); _chk(state, "state", (_F32,)); _chk(scratch, "scratch", (_F32,))
+    for t, n in ((f_b, "f_b"), (lower, "lower"), (norm_w, "norm_w")):
+        _chk(t, n, (_F32,))
+    ntok = p.shape[0]
+    if out.shape != (ntok, H * DV) or state.shape[1:] != (H, D, DV) or scratch.numel() < ntok * H * DV or norm_w.numel() != DV \
+            or f_b.numel() != H * D or lower.numel() != H * D:
+        raise ValueError("seq_hgrn2: shapes do not match")
+    _seq(_lib.load_seq().qspec_seq_hgrn2(_ptr(p), p.shape[1], _ptr(f_b), _ptr(lower), _ptr(norm_w), _ptr(state), _ptr(scratch), _ptr(out),
+                                         _ptr(meta), ntok, H, D, DV, float(eps), _sdt(p), _stream()), "seq_hgrn2")
+
+
+def seq_side_gate(g: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int) -> None:
+    """g [ntok, sd] <- gelu_tanh(g) * table[ids, col0 : col0 + sd], in place."""
+    _chk(g, "g", _SEQ_ACT); _chk(table, "table", (g.dtype,)); _chk(ids, "ids", (torch.int32,))
+    ntok, sd = g.shape
+    _seq(_lib.load_seq().qspec_seq_side_gate(_ptr(g), _ptr(table), _ptr(ids), col0, sd, table.shape[1], table.shape[0], ntok, _sdt(g),
+                                             _stream()), "seq_side_gate")

@@ -37,7 +37,7 @@ def architecture_of(cfg: dict) -> str:
 
 def supports_dtype(architecture: str, dtype: str) -> bool:
     dtype = _DTYPES.get(dtype, dtype)
-    if architecture == "Mutusun":
+    if architecture in ("Mutusun", "Pitudra"):
         return dtype in ("bfloat16", "float32")
     return dtype == "float16"          # the int4 decoders run float16 activations only
 
@@ -57,6 +57,15 @@ def _load_mutusun(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: i
     if dt is None:
         raise ValueError(f"Mutusun runs in bfloat16 or float32, not {dtype}")
     return MutusunModel.from_pretrained(path, dtype=dt, device=device, n_slots=n_slots, max_step_tokens=max_step_tokens)
+
+
+def _load_pitudra(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: int = 2048, **_):
+    import torch
+    from .pitudra import PitudraModel
+    dt = {"bfloat16": torch.bfloat16, "float32": torch.float32, None: torch.bfloat16}.get(dtype)
+    if dt is None:
+        raise ValueError(f"Pitudra runs in bfloat16 or float32, not {dtype}")
+    return PitudraModel.from_pretrained(path, dtype=dt, device=device, n_slots=n_slots, max_step_tokens=max_step_tokens)
 
 
 def _load_qspec_llama(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: int = 256, **_):
@@ -81,5 +90,6 @@ def _load_qspec_llama(path, cfg, dtype, device, n_slots: int = 8, max_step_token
 
 
 register("Mutusun", _load_mutusun)
+register("Pitudra", _load_pitudra)
 register("LlamaForCausalLM", _load_qspec_llama)
 register("Qwen2ForCausalLM", _load_qspec_llama)
