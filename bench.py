@@ -44,10 +44,11 @@ def parse():
     ap.add_argument("--no-per-layer", action="store_true")
     ap.add_argument("--agree-shifts", default="19,20,18",
                     help="embedding shifts tried for the agree-by-construction (high-acceptance) point; '' disables it")
-    ap.add_argument("--design", default="qspec", choices=["qspec", "mutusun"],
+    ap.add_argument("--design", default="qspec", choices=["qspec", "mutusun", "pitudra"],
                     help="mutusun: prefill / decode throughput and kernel rooflines of the Mutusun design next to the int4 "
-                         "decoder at equal sizes (qspec_b200/bench_seq.py); the default workload is unchanged")
-    ap.add_argument("--sizes", default="", help="--design mutusun: comma-separated size names (default: all)")
+                         "decoder at equal sizes; pitudra: the same for the Pitudra design next to Mutusun "
+                         "(qspec_b200/bench_seq.py); the default workload is unchanged")
+    ap.add_argument("--sizes", default="", help="--design mutusun / pitudra: comma-separated size names (default: all)")
     a = ap.parse_args()
     if a.seqs is None:
         a.seqs = 32 if a.model == "70b" else 64
@@ -128,9 +129,10 @@ def cpu_reference(args, seqs, budget_s, max_samples):
 
 def main():
     args = parse()
-    if args.design == "mutusun":
+    if args.design in ("mutusun", "pitudra"):
         from qspec_b200 import bench_seq
-        print(json.dumps(bench_seq.run(args, peaks(), ClockSampler)), flush=True)
+        run = bench_seq.run if args.design == "mutusun" else bench_seq.run_pitudra
+        print(json.dumps(run(args, peaks(), ClockSampler)), flush=True)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

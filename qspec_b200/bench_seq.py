@@ -1,4 +1,4 @@
-"""`bench.py --design mutusun`: prefill and decode throughput of the Mutusun design at sizes that resemble a real model's
+"""`bench.py --design mutusun` and `--design pitudra` (the second half of this file): prefill and decode throughput of the Mutusun design at sizes that resemble a real model's
 layers (random weights), next to the framework's int4 Llama decoder at equal width / heads / feed-forward size, both
 through the same scheduler; plus the design's kernels one by one against their roofline and against the like kernel of
 the int4 decoder. Prints one JSON line. The default workload of bench.py is untouched by this option.
@@ -284,6 +284,212 @@ def run(args, peaks, clock_sampler_cls) -> dict:
             "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": head["decode_ms_per_step"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (float32 residual, norms, scores)", "data": "synthetic",
             "config": {"design": "mutusun", "sizes": names, "weights": "random", "layers": 4,
+                       "l2": "kernel timings rotate buffers larger than the L2 where the kernel streams from HBM"},
+            "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src},
+            "gpu_launches": ops.seq_launch_count() - l0, "clocks": clocks, "results": out}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# `bench.py --design pitudra`: the Pitudra design (latent + grouped-query window attention, HGRN2, squared-ReLU experts)
+# next to Mutusun, the framework's closest model, at equal width / heads / expert sizes, both through the scheduler; and
+# Pitudra's kernels one by one against their roofline, with Mutusun's kernel table of the same size beside them.
+# ---------------------------------------------------------------------------------------------------------------------
+PITUDRA_SIZES = {
+    # latent attention: (q_rank, kv_rank, rot_dim); window of both attentions; side = width of the per-layer token input
+    "w2048": dict(width=2048, heads=16, kv=4, dim=128, window=1024, latent=(768, 512, 64), moe=(16, 1024, 4), side=256),
+    "w4096": dict(width=4096, heads=32, kv=8, dim=128, window=2048, latent=(1536, 512, 64), moe=(8, 2048, 2), side=256),
+}
+
+
+def pitudra_config(s):
+    H, D, win = s["heads"], s["dim"], s["window"]
+    qr, kvr, rot = s["latent"]
+    E, F, top = s["moe"]
+    moe = {"kind": "moe", "expert": {"ff": F}, "router": {"experts": E, "top": top}}
+    lat = {"heads": H, "dim": D, "vdim": D, "rot_dim": rot, "q_rank": qr, "kv_rank": kvr, "scale": (D + rot) ** -0.5, "mask": {"size": win},
+           "rot": {"base": 10000.0, "dims": rot}}
+    layers = [{"type": "latent_attention", "mixer": lat, "mlp": moe},
+              {"type": "latent_attention", "mixer": dict(lat, kv_from=0), "mlp": moe},
+              {"type": "hgrn2", "mixer": {"heads": H, "dim": D, "vdim": D}, "mlp": moe},
+              {"type": "attention", "mixer": {"heads": H, "kv_heads": s["kv"], "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": win}},
+               "mlp": moe}]
+    return {"architecture": "Pitudra", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "token_side": {"dim": s["side"]},
+            "layers": layers}
+
+
+def _pitudra_kernel_table(torch, s, hbm_gbs, bf16_tflops):
+    """Each Pitudra kernel at a prompt shape (2 048 tokens of one sequence) and a decode shape (64 sequences x 1 token with a
+    full window behind it). frac = achieved / measured peak of the binding resource."""
+    from . import ops
+    dev = "cuda"
+    W, H, G, D, win = s["width"], s["heads"], s["kv"], s["dim"], s["window"]
+    qr, kvr, rot = s["latent"]
+    E, F, top = s["moe"]
+    bf, f32 = torch.bfloat16, torch.float32
+    rows = []
+
+    def meta(segs):
+        r = [[], [], [], [], []]
+        at = 0
+        for slot, p0, n in segs:
+            r[0] += [slot] * n; r[1] += list(range(p0, p0 + n)); r[2] += [at] * n; r[3] += [at + n] * n; r[4] += [0] * n
+            at += n
+        return torch.tensor(r, dtype=torch.int32, device=dev)
+
+    def add(name, shape, us, nbytes=None, flops=None, note=None):
+        e = {"kernel": name, "shape": shape, "us": round(us, 2)}
+        if nbytes is not None:
+            e["GBps"] = round(nbytes / us / 1e3, 1); e["frac_hbm"] = round(nbytes / us / 1e3 / hbm_gbs, 3)
+        if flops is not None:
+            e["TFLOPs"] = round(flops / us / 1e6, 1); e["frac_bf16"] = round(flops / us / 1e6 / bf16_tflops, 3)
+        if note:
+            e["note"] = note
+        rows.append(e)
+
+    nslots, Tmax = 64, 2048
+    cap = win - 1 + Tmax
+    shapes = {"prompt": [(0, 0, 2048)], "decode": [(k, win + 3 * k, 1) for k in range(64)]}
+    lat_cache = [torch.randn(nslots, cap, kvr + rot, device=dev).to(bf) for _ in range(2)]
+    ck = [torch.randn(nslots, cap, G * D, device=dev).to(bf) for _ in range(2)]
+    cv = [torch.randn(nslots, cap, G * D, device=dev).to(bf) for _ in range(2)]
+    inv = (10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(dev)
+    for label, segs in shapes.items():
+        T = sum(n for _, _, n in segs)
+        tab = meta(segs)
+        nbuf = max(2, min(8, int(200e6 / (T * W * 12)) + 1))
+        x = [torch.randn(T, W, device=dev) for _ in range(nbuf)]
+        y = [torch.randn(T, W, device=dev).to(bf) for _ in range(nbuf)]
+        h = [torch.empty(T, W, device=dev, dtype=bf) for _ in range(nbuf)]
+        wv, bv = torch.ones(W, device=dev), torch.zeros(W, device=dev)
+        prev = torch.zeros(2, nslots, W, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.seq_token_shift(x[i], bv, prev, h[i], tab) for i in range(nbuf)])
+        add("seq_token_shift", f"{label} T={T} W={W}", us, nbytes=T * W * 6)
+        us = _time_us(torch, [lambda i=i: ops.seq_add_norm(y[i], wv, bv, 1e-5, x_in=x[i], x_out=x[i], out=h[i]) for i in range(nbuf)])
+        add("seq_add_norm (residual + layer norm of the output + cast)", f"{label} T={T} W={W}", us, nbytes=T * W * 12)
+        pair = [torch.randn(T, top, W, device=dev).to(bf) for _ in range(2)]
+        rw = torch.rand(T, top, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.seq_add_norm(pair[i % 2], wv, bv, 1e-5, x_in=x[i], x_out=x[i], out=h[i], y_w=rw) for i in range(nbuf)])
+        add("seq_add_norm (weighted sum of the experts' parts)", f"{label} T={T} top={top}", us, nbytes=T * W * (10 + 2 * top))
+        # latent attention
+        ld = qr + kvr + rot
+        dd = [(torch.randn(T, ld, device=dev)).to(bf) for _ in range(nbuf)]
+        cq = torch.empty(T, qr, device=dev, dtype=bf)
+        us = _time_us(torch, [lambda i=i: ops.seq_latent_prep(dd[i], qr, kvr, rot, wv[:qr].contiguous(), wv[:kvr].contiguous(), inv, rot, cq,
+                                                              lat_cache[i % 2], tab, 1e-5) for i in range(nbuf)])
+        add("seq_latent_prep (2 norms + rotary + cache rows)", f"{label} T={T}", us, nbytes=T * (ld * 2 + qr * 2 + (kvr + rot) * 2))
+        q = [(torch.randn(T, H, D + rot, device=dev) * 0.3).to(bf) for _ in range(2)]
+        qb = torch.empty(T, H, rot, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.seq_rotary(q[i % 2], D, qb, rot, inv, tab) for i in range(2)])
+        add("seq_rotary (query part)", f"{label} T={T} H={H}", us, nbytes=T * H * rot * 6)
+        qa = [torch.randn(H, T, kvr, device=dev) * 0.05 for _ in range(2)]
+        olat = torch.empty(T, H, kvr, device=dev, dtype=bf)
+        sink = torch.zeros(H, device=dev)
+        visible = sum(min(p + 1, win) for _, p0, n in segs for p in range(p0, p0 + n))
+
+        def lat_attn(i):
+            c = lat_cache[i % 2].unsqueeze(2)
+            ops.seq_window_attention(qa[i % 2].transpose(0, 1), qb, c, c[..., :kvr], olat, tab, win, 0.07, sink=sink)
+        us = _time_us(torch, [lambda i=i: lat_attn(i) for i in range(2)], reps=6 if label == "prompt" else 20)
+        if label == "prompt":
+            add("seq_window_attention, latent form", f"T={T} window={win} H={H} key {kvr}+{rot} value {kvr}", us,
+                flops=2.0 * visible * H * (2 * kvr + rot), note="one CTA per (token, head), float32 lanes: no tensor cores yet")
+        else:
+            add("seq_window_attention, latent form", f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * (kvr + rot) * 2)
+        # grouped-query attention
+        ldq = H * D + 2 * G * D + H * D
+        pq = [(torch.randn(T, ldq, device=dev) * 0.3).to(bf) for _ in range(nbuf)]
+        qf = [torch.empty(T, H * D, device=dev) for _ in range(2)]
+        wq = torch.ones(H * D, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.seq_qkv_prep(pq[i], H * D, G * D, G * D, wq, wq[:G * D].contiguous(), qf[i % 2], ck[i % 2], cv[i % 2],
+                                                           tab, 1e-5) for i in range(nbuf)])
+        add("seq_qkv_prep (2 norms + cache rows)", f"{label} T={T}", us, nbytes=T * ((H + 2 * G) * D * 2 + H * D * 4 + 2 * G * D * 2))
+        att = torch.empty(T, H, D, device=dev, dtype=bf)
+
+        def gqa(i):
+            ops.seq_window_attention(qf[i % 2].view(T, H, D), None, ck[i % 2].view(nslots, cap, G, D), cv[i % 2].view(nslots, cap, G, D), att,
+                                     tab, win, D ** -0.5, sink=sink, gate=pq[i % nbuf][:, H * D + 2 * G * D:])
+        us = _time_us(torch, [lambda i=i: gqa(i) for i in range(2)], reps=6 if label == "prompt" else 20)
+        if label == "prompt":
+            add("seq_window_attention, grouped-query form + gate", f"T={T} window={win} H={H} G={G} D={D}", us, flops=2.0 * visible * H * 2 * D,
+                note="one CTA per (token, head), float32 lanes: no tensor cores yet")
+        else:
+            add("seq_window_attention, grouped-query form + gate", f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * G * 2 * D * 2)
+        # recurrence
+        ldr = H * 3 * D
+        pr = [(torch.randn(T, ldr, device=dev)).to(bf) for _ in range(nbuf)]
+        state = torch.zeros(nslots, H, D, D, device=dev)
+        scr = torch.empty(T * H * D, device=dev)
+        orec = torch.empty(T, H * D, device=dev, dtype=bf)
+        fb, lo = torch.zeros(H * D, device=dev), torch.full((H * D,), 0.5, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.seq_hgrn2(pr[i], fb, lo, wv[:D].contiguous(), state, scr, orec, tab, H, D, D, 1e-5) for i in range(nbuf)])
+        nseg = len(segs)
+        add("seq_hgrn2 (scan + head norm)", f"{label} T={T} H={H} D={D}", us,
+            nbytes=T * (ldr * 2 + H * D * 10) + (2 * nseg * H * D * D * 4 if label == "decode" else 0), flops=4.0 * T * H * D * D,
+            note="sequential over a sequence's tokens: H x D/32 CTAs per sequence" if label == "prompt" else None)
+        # router and experts
+        hb = [torch.randn(T, W, device=dev).to(bf) for _ in range(nbuf)]
+        rwt = torch.randn(E, W, device=dev) * 0.05
+        idx = torch.empty(T, top, dtype=torch.int32, device=dev)
+        wt = torch.empty(T, top, device=dev)
+        us = _time_us(torch, [lambda i=i: ops.moe_route_chosen(hb[i], rwt, idx, wt) for i in range(nbuf)])
+        add("moe_route_chosen", f"{label} T={T} R={E}", us, nbytes=T * W * 2)
+        up = [(torch.randn(E, F, W, device=dev) * W ** -0.5).to(bf) for _ in range(2)]
+        dn = [(torch.randn(E, W, F, device=dev) * F ** -0.5).to(bf) for _ in range(2)]
+        pr2 = torch.empty(T, top, W, device=dev, dtype=bf)
+        us = _time_us(torch, [lambda i=i: ops.moe_expert_grouped(hb[i % nbuf], up[i % 2], dn[i % 2], idx, pr2, E, F, 0.0, act="relu2") for i in range(2)])
+        if label == "prompt":
+            add("moe_expert_grouped, squared ReLU (sort + 2 tile GEMMs)", f"T={T} top={top} E={E} F={F}", us, flops=2.0 * T * top * 2 * W * F)
+        else:
+            touched = len(set(idx.flatten().tolist()))
+            add("moe_expert_grouped, squared ReLU (sort + 2 tile GEMMs)", f"T={T} top={top}, {touched} of {E} experts touched", us,
+                nbytes=touched * 2 * W * F * 2)
+        del x, y, h, pair, dd, q, qa, pq, qf, pr, hb, up, dn
+    return rows
+
+
+def run_pitudra(args, peaks, clock_sampler_cls) -> dict:
+    import torch
+    from . import ops
+    from .build import build_seq_library
+    from .mutusun import MutusunConfig, MutusunModel, random_weights as mutusun_weights
+    from .pitudra import PitudraConfig, PitudraModel, random_weights
+    from .scheduler import Scheduler
+    build_seq_library()
+    torch.cuda.set_device(0)
+    hbm_gbs, bf16_tflops, peak_src = peaks
+    bf16_tflops = bf16_tflops or 1590.0
+    names = [n for n in (args.sizes.split(",") if args.sizes else PITUDRA_SIZES) if n in PITUDRA_SIZES]
+    steps, warmup = args.steps, max(3, args.warmup)
+    out = {}
+    sampler = clock_sampler_cls(0)
+    sampler.start()
+    l0 = ops.seq_launch_count()
+    for name in names:
+        s = PITUDRA_SIZES[name]
+        res = {"layers": 4, "sizes": s}
+        cfg = PitudraConfig.from_dict(pitudra_config(s))
+        model = PitudraModel(cfg, random_weights(cfg, 0), dtype=torch.bfloat16, device="cuda", n_slots=65, max_step_tokens=2048)
+        res["pitudra"] = {p: _throughput(torch, Scheduler(model, prefill_portion=p), VOCAB, 64, s["window"] + 300, 4096, p, steps, warmup)
+                          for p in (2048, 256)}
+        res["pitudra"]["state_bytes_per_sequence"] = model.state_bytes_per_slot()
+        del model
+        torch.cuda.empty_cache()
+        mcfg = MutusunConfig.from_dict(mutusun_config(SIZES[name]))
+        mut = MutusunModel(mcfg, mutusun_weights(mcfg, 0), dtype=torch.bfloat16, device="cuda", n_slots=65, max_step_tokens=2048)
+        res["mutusun"] = {p: _throughput(torch, Scheduler(mut, prefill_portion=p), VOCAB, 64, s["window"] + 300, 4096, p, steps, warmup)
+                          for p in (2048, 256)}
+        res["mutusun"]["state_bytes_per_sequence"] = mut.state_bytes_per_slot()
+        del mut
+        torch.cuda.empty_cache()
+        res["kernels"] = _pitudra_kernel_table(torch, s, hbm_gbs, bf16_tflops)
+        res["like_kernels_mutusun"] = _kernel_table(torch, SIZES[name], hbm_gbs, bf16_tflops)
+        out[name] = res
+    clocks = sampler.stop()
+    head = out[names[-1]]["pitudra"][2048]
+    return {"metric": "pitudra_prefill_decode_tokens_per_s", "value": head["decode_tokens_per_s"], "unit": "tokens/s (decode, 64 sequences)",
+            "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": head["decode_ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (float32 residual, norms, scores, recurrence)", "data": "synthetic",
+            "config": {"design": "pitudra", "sizes": names, "weights": "random", "layers": 4,
                        "l2": "kernel timings rotate buffers larger than the L2 where the kernel streams from HBM"},
             "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src},
             "gpu_launches": ops.seq_launch_count() - l0, "clocks": clocks, "results": out}
