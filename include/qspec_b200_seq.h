@@ -175,6 +175,16 @@ typedef struct qspec_window_attn_args {
 } qspec_window_attn_args;
 int qspec_seq_window_attention(const qspec_window_attn_args* args, int dtype, void* stream);
 
+/* The same attention on the tensor cores (bfloat16; key parts 64 or 128 (+ a shared part of 64 with a per-head part of
+ * 128), value size 64 or 128; rows and strides on 16-byte boundaries). args->qa is the whole query [DA] (args->DB = 0); the
+ * last DB entries of a key come from k_shared (one row per slot and ring row, shared by all heads: the rotary part of a
+ * latent cache), the first DA - DB from args->k. token_rows = 0: one CTA per (token, key/value head), the rows of the
+ * products are the query heads of the group (H / G <= 16) -- decode-shaped batches; 1: one CTA per (16 consecutive batch
+ * tokens, head) -- prompts. */
+int qspec_seq_window_attention_mma(const qspec_window_attn_args* args, const void* k_shared, long long k_shared_slot_stride,
+                                   int k_shared_row_stride, int DB, int token_rows, void* stream);
+int qspec_seq_window_attention_mma_supported(int DA, int DB, int DV, int H, int G, int token_rows);
+
 /* HGRN2 recurrence. Row t of p = [zq (H x D) | zf (H x D) | v (H x DV)]. q = silu(zq), f = lower + (1 - lower) *
  * sigmoid(zf + f_b); per head S <- diag(f) S + (1 - f) v^T, o = S^T q; out[t, h] = unit_rms(o over DV) * norm_w.
  * state: float32 [slots, H, D, DV], read at a segment's start (zero at position 0), written at its end.

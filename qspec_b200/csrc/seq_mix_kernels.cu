@@ -181,9 +181,9 @@ qkv_prep_kernel(const T* __restrict__ p, int ld, int HD, int GD, int GDV, const 
 // ---- sliding-window softmax attention with a sink -------------------------------------------------------------------
 // One CTA of four warps per (token, query head). Query = two float32 parts (qa against key[0:DA], qb against
 // key[DA:DA+DB]); keys and values are rows of a per-slot ring (row = position % cap) that already holds the step's
-// own tokens. A warp takes every fourth key of the window: lanes along the row for the dot product, an online softmax
-// per warp, and the four partial results are merged in shared memory together with the sink term exp(sink[h]) of the
-// denominator. Which warp takes which key depends on the token's position only, so a token's result does not depend
+// own tokens. A warp takes every fourth run of four keys of the window: lanes along the rows for the dot products, an
+// online softmax per warp, and the four partial results are merged in shared memory together with the sink term
+// exp(sink[h]) of the denominator. Which warp takes which key depends on the token's position only, so a token's result does not depend
 // on how its sequence was cut into steps or on its neighbours in the batch.
 template <typename T, int NACC, int VEC>
 __global__ void __launch_bounds__(128)
@@ -211,29 +211,58 @@ window_attn_kernel(const float* __restrict__ qa, long long qa_ts, long long qa_h
   float acc[NACC];
 #pragma unroll
   for (int a = 0; a < NACC; ++a) acc[a] = 0.f;
-  for (int j = j0 + warp; j <= pos; j += 4) {
-    const int r = j % cap;
-    const T* kr = kbase + (size_t)r * k_rs;
-    float dot = 0.f;
-    for (int c = lane * VEC; c < DK; c += 32 * VEC) {
-      float kv[2];
-      ld_pair<VEC>(kr + c, kv);
-      dot += sq[c] * kv[0];
-      if (VEC == 2) dot += sq[c + 1] * kv[1];
+  // a warp takes runs of KU consecutive keys (every fourth run): KU independent rows in flight per iteration
+  constexpr int KU = 4;
+  for (int j = j0 + warp * KU; j <= pos; j += 4 * KU) {
+    const int n = min(KU, pos - j + 1);
+    const T* kr[KU];
+    const T* vr[KU];
+#pragma unroll
+    for (int u = 0; u < KU; ++u) {
+      const int r = (j + (u < n ? u : 0)) % cap;
+      kr[u] = kbase + (size_t)r * k_rs;
+      vr[u] = vbase + (size_t)r * v_rs;
     }
-    const float s = warp_xor_sum(dot) * scale;
-    const float mn = fmaxf(m, s);
-    const float corr = expf(m - mn), p = expf(s - mn);
+    float dot[KU];
+#pragma unroll
+    for (int u = 0; u < KU; ++u) dot[u] = 0.f;
+    for (int c = lane * VEC; c < DK; c += 32 * VEC) {
+      const float q0 = sq[c], q1 = VEC == 2 ? sq[c + 1] : 0.f;
+#pragma unroll
+      for (int u = 0; u < KU; ++u) {
+        float kv[2];
+        ld_pair<VEC>(kr[u] + c, kv);
+        dot[u] += q0 * kv[0];
+        if (VEC == 2) dot[u] += q1 * kv[1];
+      }
+    }
+    float mn = m;
+#pragma unroll
+    for (int u = 0; u < KU; ++u) {
+      dot[u] = u < n ? warp_xor_sum(dot[u]) * scale : -INFINITY;
+      mn = fmaxf(mn, dot[u]);
+    }
+    const float corr = expf(m - mn);
+    float p[KU], ps = 0.f;
+#pragma unroll
+    for (int u = 0; u < KU; ++u) { p[u] = expf(dot[u] - mn); ps += p[u]; }
     m = mn;
-    l = l * corr + p;
-    const T* vr = vbase + (size_t)r * v_rs;
+    l = l * corr + ps;
 #pragma unroll
     for (int a = 0; a < NACC; a += VEC) {
       const int c = lane * VEC + 32 * a;
-      float vv[2] = {0.f, 0.f};
-      if (c < DV) ld_pair<VEC>(vr + c, vv);
-      acc[a] = acc[a] * corr + p * vv[0];
-      if (VEC == 2) acc[a + 1] = acc[a + 1] * corr + p * vv[1];
+      float s0 = 0.f, s1 = 0.f;
+      if (c < DV) {
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+          float vv[2];
+          ld_pair<VEC>(vr[u] + c, vv);
+          s0 += p[u] * vv[0];
+          s1 += p[u] * vv[1];
+        }
+      }
+      acc[a] = acc[a] * corr + s0;
+      if (VEC == 2) acc[a + 1] = acc[a + 1] * corr + s1;
     }
   }
   if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }

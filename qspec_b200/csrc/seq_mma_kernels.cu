@@ -952,3 +952,269 @@ extern "C" int qspec_moe_expert_grouped(const void* h, const void* gate_up, cons
   return qspec_moe_expert_grouped_act(h, gate_up, down, idx, out, ntok, W, F, E, top, limit, QSPEC_EXPERT_ACT_GATED, workspace,
                                       workspace_bytes, stream);
 }
+
+namespace qspec {
+// ---------------------------------------------------------------------------------------------------------------------
+// Sliding-window softmax attention with a sink on the tensor cores (bfloat16 keys / values in per-slot rings).
+// One CTA (4 warps) per block of 16 rows; the rows of both products are either the query heads that share a key/value
+// head, for one token (decode-shaped batches), or 16 consecutive batch tokens for one head (prompts). The four warps
+// take every fourth step of 16 keys of the visible range, each with its own online softmax (float32 maxima and sums),
+// and their partial results are merged in shared memory together with the sink term. As in the token form above, K and
+// V rows go from global memory straight into the mma.sync fragments with 16-byte loads (the summation index of both
+// products is permuted instead of transposing through shared memory), the next step's rows in flight while the current
+// one is multiplied. A key is two parts: [0, DA) from kA (per key/value head) and [DA, DA + DB) from kB (shared by all
+// heads: the rotary part of a latent cache). Weights are float32 and enter the second product as a two-term bfloat16
+// split. A block of tokens may span several sequences: their key ranges are walked one after the other.
+// ---------------------------------------------------------------------------------------------------------------------
+struct WinMma {
+  const float* q; long long q_ts, q_hs;
+  const bf16* kA; long long kA_ss; int kA_rs, kA_hs;
+  const bf16* kB; long long kB_ss; int kB_rs;
+  const bf16* v; long long v_ss; int v_rs, v_hs;
+  const float* sink; const bf16* gate; int gate_ld;
+  bf16* out; const int* meta; int ntok, H, G, window, cap; float scale; int token_rows;
+};
+
+template <int DA, int DB, int DV>
+__global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a) {
+  pdl_enter();
+  constexpr int DK = DA + DB, QS = DK / 2 + 4;
+  extern __shared__ __align__(16) unsigned char wm_raw[];
+  uint32_t* sQ = reinterpret_cast<uint32_t*>(wm_raw);       // [16][QS]
+  float* sO = reinterpret_cast<float*>(sQ + 16 * QS);        // [4 warps][16][DV]
+  __shared__ float sM[4][16], sL[4][16];
+  __shared__ int s_tok[16], s_head[16], s_pos[16], s_seg[16], s_slot[16];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int rep = a.H / a.G;
+  const int kvh = a.token_rows ? (int)blockIdx.y / rep : (int)blockIdx.y;
+  if (tid < 16) {
+    int tok = -1, head = 0;
+    if (a.token_rows) { tok = blockIdx.x * 16 + tid; head = blockIdx.y; if (tok >= a.ntok) tok = -1; }
+    else if (tid < rep) { tok = blockIdx.x; head = kvh * rep + tid; }
+    s_tok[tid] = tok; s_head[tid] = head;
+    s_pos[tid] = tok >= 0 ? a.meta[a.ntok + tok] : -1;
+    s_seg[tid] = tok >= 0 ? a.meta[2 * a.ntok + tok] : -1;
+    s_slot[tid] = tok >= 0 ? a.meta[tok] : 0;
+  }
+  __syncthreads();
+  for (int c = tid; c < 16 * (DK / 2); c += 128) {
+    const int row = c / (DK / 2), w = c - row * (DK / 2);
+    uint32_t val = 0u;
+    if (s_tok[row] >= 0) {
+      const float2 f = *reinterpret_cast<const float2*>(a.q + (size_t)s_tok[row] * a.q_ts + (size_t)s_head[row] * a.q_hs + 2 * w);
+      val = pack_bf2(f.x, f.y);
+    }
+    sQ[row * QS + w] = val;
+  }
+  __syncthreads();
+  const int rA = gid, rB = gid + 8;
+  const int posA = s_pos[rA], posB = s_pos[rB], segA = s_seg[rA], segB = s_seg[rB];
+  float o[DV / 8][4];
+#pragma unroll
+  for (int t = 0; t < DV / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  struct Rows { uint4 k[2][DK / 32]; uint4 v[4][DV / 64]; };
+
+  int r0 = 0;
+  while (r0 < 16 && s_tok[r0] >= 0) {
+    // rows r0 .. r1 - 1 belong to one sequence (token rows), or all rows to the one token (head rows)
+    int r1 = r0 + 1;
+    while (r1 < 16 && s_tok[r1] >= 0 && s_seg[r1] == s_seg[r0]) ++r1;
+    const int seg = s_seg[r0], slot = s_slot[r0];
+    const int pmax = a.token_rows ? s_pos[r1 - 1] : s_pos[r0];
+    const int jlo = max(0, s_pos[r0] - a.window + 1);
+    const int nkeys = pmax - jlo + 1;
+    const bf16* kA = a.kA + (size_t)slot * a.kA_ss + (size_t)kvh * a.kA_hs;
+    const bf16* kB = DB ? a.kB + (size_t)slot * a.kB_ss : nullptr;
+    const bf16* vb = a.v + (size_t)slot * a.v_ss + (size_t)kvh * a.v_hs;
+    auto fetch = [&](int hb, Rows& r) {
+      const int kb = hb * 16;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int jj = kb + 8 * nt + gid;
+        const bool ok = jj < nkeys;
+        const int row = ok ? (jlo + jj) % a.cap : 0;
+        const bf16* kp = kA + (size_t)row * a.kA_rs;
+#pragma unroll
+        for (int j = 0; j < DA / 32; ++j) r.k[nt][j] = ok ? __ldg(reinterpret_cast<const uint4*>(kp + 32 * j + 8 * tig)) : zero4;
+        if (DB) {
+          const bf16* kq = kB + (size_t)row * a.kB_rs;
+#pragma unroll
+          for (int j = 0; j < DB / 32; ++j) r.k[nt][DA / 32 + j] = ok ? __ldg(reinterpret_cast<const uint4*>(kq + 32 * j + 8 * tig)) : zero4;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int jj = kb + 2 * tig + (q & 1) + 8 * (q >> 1);
+        const bool ok = jj < nkeys;
+        const bf16* vp = vb + (size_t)(ok ? (jlo + jj) % a.cap : 0) * a.v_rs;
+#pragma unroll
+        for (int sp = 0; sp < DV / 64; ++sp) r.v[q][sp] = ok ? __ldg(reinterpret_cast<const uint4*>(vp + 64 * sp + 8 * gid)) : zero4;
+      }
+    };
+    const bool inA = a.token_rows ? (segA == seg && s_tok[rA] >= 0) : rA < rep;
+    const bool inB = a.token_rows ? (segB == seg && s_tok[rB] >= 0) : rB < rep;
+    Rows cur, nxt;
+    int hb = warp;
+    if (hb * 16 < nkeys) fetch(hb, cur);
+    for (; hb * 16 < nkeys; hb += 4) {
+      const int kb = hb * 16;
+      if ((hb + 4) * 16 < nkeys) fetch(hb + 4, nxt);
+      float s[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int j = 0; j < DK / 32; ++j)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int wq = 16 * j + 4 * tig + 2 * half;
+          const uint32_t af[4] = {sQ[gid * QS + wq], sQ[(gid + 8) * QS + wq], sQ[gid * QS + wq + 1], sQ[(gid + 8) * QS + wq + 1]};
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+            mma_bf16_16816(s[nt], af, half ? cur.k[nt][j].z : cur.k[nt][j].x, half ? cur.k[nt][j].w : cur.k[nt][j].y);
+        }
+      // visible: same sequence, key position <= the row's and within its window
+      float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int pj = jlo + kb + 8 * nt + 2 * tig + (c & 1);
+          const int pr = (c >> 1) ? posB : posA;
+          const bool vis = ((c >> 1) ? inB : inA) && pj <= pr && pr - pj < a.window && pj <= pmax;
+          s[nt][c] = vis ? s[nt][c] * a.scale : -INFINITY;
+          if (c >> 1) mxB = fmaxf(mxB, s[nt][c]); else mxA = fmaxf(mxA, s[nt][c]);
+        }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1)); mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+      const float cA = nA == -INFINITY ? 1.f : __expf(mA - nA), cB = nB == -INFINITY ? 1.f : __expf(mB - nB);
+      const float bA = nA == -INFINITY ? 0.f : nA, bB = nB == -INFINITY ? 0.f : nB;
+      mA = nA; mB = nB;
+      float w[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) w[nt][c] = __expf(s[nt][c] - ((c >> 1) ? bB : bA));      // exp(-inf) = 0 for hidden keys
+      lA = lA * cA + (w[0][0] + w[0][1]) + (w[1][0] + w[1][1]);
+      lB = lB * cB + (w[0][2] + w[0][3]) + (w[1][2] + w[1][3]);
+#pragma unroll
+      for (int t = 0; t < DV / 8; ++t) { o[t][0] *= cA; o[t][1] *= cA; o[t][2] *= cB; o[t][3] *= cB; }
+      uint32_t ah[4], al[4];
+      split_bf2(w[0][0], w[0][1], ah[0], al[0]);
+      split_bf2(w[0][2], w[0][3], ah[1], al[1]);
+      split_bf2(w[1][0], w[1][1], ah[2], al[2]);
+      split_bf2(w[1][2], w[1][3], ah[3], al[3]);
+#pragma unroll
+      for (int sp = 0; sp < DV / 64; ++sp) {
+        const uint32_t v0[4] = {cur.v[0][sp].x, cur.v[0][sp].y, cur.v[0][sp].z, cur.v[0][sp].w};
+        const uint32_t v1[4] = {cur.v[1][sp].x, cur.v[1][sp].y, cur.v[1][sp].z, cur.v[1][sp].w};
+        const uint32_t v2[4] = {cur.v[2][sp].x, cur.v[2][sp].y, cur.v[2][sp].z, cur.v[2][sp].w};
+        const uint32_t v3[4] = {cur.v[3][sp].x, cur.v[3][sp].y, cur.v[3][sp].z, cur.v[3][sp].w};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const uint32_t sel = (t & 1) ? 0x7632u : 0x5410u;
+          const uint32_t b0 = __byte_perm(v0[t >> 1], v1[t >> 1], sel), b1 = __byte_perm(v2[t >> 1], v3[t >> 1], sel);
+          mma_bf16_16816(o[sp * 8 + t], ah, b0, b1);
+          mma_bf16_16816(o[sp * 8 + t], al, b0, b1);
+        }
+      }
+      cur = nxt;
+    }
+    if (!a.token_rows) break;
+    r0 = r1;
+  }
+  // the warp's sums: each thread holds a quarter of its rows' sums of weights
+  lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+  lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+  if (tig == 0) { sM[warp][rA] = mA; sL[warp][rA] = lA; sM[warp][rB] = mB; sL[warp][rB] = lB; }
+  // tile (sp, t), register c -> row gid + 8 (c >> 1), d = 64 sp + 8 (2 tig + (c & 1)) + t
+#pragma unroll
+  for (int sp = 0; sp < DV / 64; ++sp)
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        sO[(warp * 16 + gid + 8 * (c >> 1)) * DV + 64 * sp + 8 * (2 * tig + (c & 1)) + t] = o[sp * 8 + t][c];
+  __syncthreads();
+  for (int e = tid; e < 16 * DV; e += 128) {
+    const int row = e / DV, d = e - row * DV;
+    const int tok = s_tok[row];
+    if (tok < 0) continue;
+    const int head = s_head[row];
+    float M = a.sink ? a.sink[head] : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w][row]);
+    float L = a.sink ? __expf(a.sink[head] - M) : 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = sM[w][row] == -INFINITY ? 0.f : __expf(sM[w][row] - M);
+      L += sL[w][row] * f;
+      acc += sO[(w * 16 + row) * DV + d] * f;
+    }
+    float r = acc / L;
+    if (a.gate) r *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(a.gate[(size_t)tok * a.gate_ld + (size_t)head * DV + d])));
+    a.out[((size_t)tok * a.H + head) * DV + d] = __float2bfloat16_rn(r);
+  }
+}
+
+template <int DA, int DB, int DV>
+static int launch_window_mma(const WinMma& a, cudaStream_t st) {
+  constexpr size_t smem = (size_t)16 * ((DA + DB) / 2 + 4) * 4 + (size_t)4 * 16 * DV * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<DA, DB, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  const dim3 grid = a.token_rows ? dim3((a.ntok + 15) / 16, a.H) : dim3(a.ntok, a.G);
+  launch_pdl(window_attn_mma_kernel<DA, DB, DV>, grid, dim3(128), smem, st, a);
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
+// Entry for qspec_seq_window_attention_mma (below) and for seq_mix_kernels.cu: -1 when the shape is not one this form takes.
+int window_attention_mma(const qspec_window_attn_args* p, const void* kB, long long kB_ss, int kB_rs, int DB, int token_rows,
+                         cudaStream_t st) {
+  const int DA = p->DA, DV = p->DV;
+  const bool shape = (DB == 0 && (DA == 64 || DA == 128) && (DV == 64 || DV == 128)) || (DA == 128 && DB == 64 && DV == 128);
+  const bool ok = shape && p->H % p->G == 0 && (token_rows || p->H / p->G <= 16) && p->H <= 65535 && p->G <= 65535 &&
+                  p->k_row_stride % 8 == 0 && p->k_head_stride % 8 == 0 && p->k_slot_stride % 8 == 0 && p->v_row_stride % 8 == 0 &&
+                  p->v_head_stride % 8 == 0 && p->v_slot_stride % 8 == 0 && kB_rs % 8 == 0 && kB_ss % 8 == 0 &&
+                  p->qa_tok_stride % 2 == 0 && p->qa_head_stride % 2 == 0 &&
+                  (((uintptr_t)p->k | (uintptr_t)p->v | (uintptr_t)kB) & 15) == 0 && ((uintptr_t)p->qa & 7) == 0;
+  if (!ok) return -1;
+  WinMma a;
+  a.q = p->qa; a.q_ts = p->qa_tok_stride; a.q_hs = p->qa_head_stride;
+  a.kA = (const bf16*)p->k; a.kA_ss = p->k_slot_stride; a.kA_rs = p->k_row_stride; a.kA_hs = p->k_head_stride;
+  a.kB = (const bf16*)kB; a.kB_ss = kB_ss; a.kB_rs = kB_rs;
+  a.v = (const bf16*)p->v; a.v_ss = p->v_slot_stride; a.v_rs = p->v_row_stride; a.v_hs = p->v_head_stride;
+  a.sink = p->sink; a.gate = (const bf16*)p->gate; a.gate_ld = p->gate_ld;
+  a.out = (bf16*)p->out; a.meta = p->meta; a.ntok = p->ntok; a.H = p->H; a.G = p->G; a.window = p->window; a.cap = p->cap;
+  a.scale = p->scale; a.token_rows = token_rows;
+  if (DB) return launch_window_mma<128, 64, 128>(a, st);
+  if (DA == 64 && DV == 64) return launch_window_mma<64, 0, 64>(a, st);
+  if (DA == 64) return launch_window_mma<64, 0, 128>(a, st);
+  if (DV == 64) return launch_window_mma<128, 0, 64>(a, st);
+  return launch_window_mma<128, 0, 128>(a, st);
+}
+}  // namespace qspec
+
+extern "C" int qspec_seq_window_attention_mma(const qspec_window_attn_args* args, const void* k_shared, long long k_shared_slot_stride,
+                                              int k_shared_row_stride, int DB, int token_rows, void* stream) {
+  QSPEC_REQUIRE(args && args->qa && args->k && args->v && args->out && args->meta && (DB == 0 || k_shared), QSPEC_ERR_INVALID_ARG,
+                "seq_window_attention_mma: null pointer");
+  QSPEC_REQUIRE(args->DB == 0, QSPEC_ERR_INVALID_ARG, "seq_window_attention_mma: the query is one part here (DA = the whole key size)");
+  if (args->ntok == 0) return QSPEC_OK;
+  qspec_window_attn_args p = *args;
+  p.DA = args->DA - DB;                                   // size of the per-head key part
+  const int s = qspec::window_attention_mma(&p, k_shared, k_shared_slot_stride, k_shared_row_stride, DB, token_rows, (cudaStream_t)stream);
+  QSPEC_REQUIRE(s >= 0, QSPEC_ERR_UNSUPPORTED, "seq_window_attention_mma: key parts %d + %d, value size %d, or strides / alignment not taken",
+                args->DA - DB, DB, args->DV);
+  return s;
+}
+
+extern "C" int qspec_seq_window_attention_mma_supported(int DA, int DB, int DV, int H, int G, int token_rows) {
+  const bool shape = (DB == 0 && (DA == 64 || DA == 128) && (DV == 64 || DV == 128)) || (DA == 128 && DB == 64 && DV == 128);
+  return shape && G > 0 && H % G == 0 && (token_rows || H / G <= 16);
+}

@@ -979,13 +979,14 @@ def seq_latent_prep(d: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, qn
 
 
 def seq_rotary(src: torch.Tensor, off: int, dst: torch.Tensor, rot_dims: int, inv_freq: torch.Tensor, meta: torch.Tensor) -> None:
-    """dst [ntok, H, n] float32 = rotary positions on src[t, h, off : off + n] (src [ntok, H, head size])."""
-    _chk(src, "src", _SEQ_ACT); _chk(dst, "dst", (_F32,)); _chk(inv_freq, "inv_freq", (_F32,))
+    """dst [ntok, H, n] float32 (a view with a unit last stride will do) = rotary positions on src[t, h, off : off + n]
+    (src [ntok, H, head size])."""
+    _chk(src, "src", _SEQ_ACT); _chk(inv_freq, "inv_freq", (_F32,))
     ntok, H, n = dst.shape
-    if src.shape[:2] != (ntok, H) or off + n > src.shape[2]:
+    if dst.dtype != _F32 or not dst.is_cuda or dst.stride(2) != 1 or src.shape[:2] != (ntok, H) or off + n > src.shape[2]:
         raise ValueError("seq_rotary: shapes do not match")
-    _seq(_lib.load_seq().qspec_seq_rotary(_ptr(src), H * src.shape[2], src.shape[2], off, _ptr(dst), H * n, n, H, n, rot_dims,
-                                          _ptr(inv_freq), _ptr(meta), ntok, _sdt(src), _stream()), "seq_rotary")
+    _seq(_lib.load_seq().qspec_seq_rotary(_ptr(src), H * src.shape[2], src.shape[2], off, dst.data_ptr(), dst.stride(0), dst.stride(1), H,
+                                          n, rot_dims, _ptr(inv_freq), _ptr(meta), ntok, _sdt(src), _stream()), "seq_rotary")
 
 
 def seq_qkv_prep(p: torch.Tensor, HD: int, GD: int, GDV: int, qn_w: torch.Tensor, kn_w: torch.Tensor, qout: torch.Tensor,
@@ -1032,6 +1033,45 @@ def seq_window_attention(qa: torch.Tensor, qb: Optional[torch.Tensor], cache_k: 
                             _ptr(sink), gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
                             _ptr(out), _ptr(meta), ntok, H, G, int(window), cap, float(scale))
     _seq(_lib.load_seq().qspec_seq_window_attention(ctypes.byref(a), _sdt(out), _stream()), "seq_window_attention")
+
+
+def seq_window_attention_mma_supported(out_dtype, DA: int, DB: int, DV: int, H: int, G: int, token_rows: bool) -> bool:
+    """The tensor-core form takes bfloat16 caches with per-head key parts of 64 or 128 (128 with a shared part of 64) and
+    values of 64 or 128; with heads as rows, at most 16 query heads per key/value head."""
+    return bool(out_dtype == _BF16 and _lib.load_seq().qspec_seq_window_attention_mma_supported(DA, DB, DV, H, G, int(token_rows)))
+
+
+def seq_window_attention_mma(q: torch.Tensor, cache_k: torch.Tensor, k_shared: Optional[torch.Tensor], cache_v: torch.Tensor,
+                             out: torch.Tensor, meta: torch.Tensor, window: int, scale: float, token_rows: bool,
+                             sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+    """`seq_window_attention` on the tensor cores (bfloat16). q [ntok, H, DK] float32; cache_k [slots, cap, G, DA] holds the
+    per-head part of the keys and k_shared [slots, cap, DB] (or None) the part all heads share, DK = DA + DB; cache_v
+    [slots, cap, G, DV] (views: a slot stride of 0 serves one buffer to every slot). token_rows: False = the rows of the
+    products are the query heads of a group, one CTA per (token, key/value head): decoding; True = 16 consecutive batch
+    tokens per CTA and head: prompts."""
+    import ctypes
+    if q.dtype != _F32 or cache_k.dtype != _BF16 or cache_v.dtype != _BF16 or out.dtype != _BF16:
+        raise ValueError("seq_window_attention_mma: float32 queries, bfloat16 caches and output")
+    _chk(out, "out", (_BF16,))
+    ntok, H, DK = q.shape
+    slots, cap, G, DA = cache_k.shape
+    DB = k_shared.shape[2] if k_shared is not None else 0
+    DV = cache_v.shape[3]
+    if DK != DA + DB or out.shape != (ntok, H, DV) or cache_v.shape[:3] != (slots, cap, G) or meta.shape != (5, ntok) \
+            or (k_shared is not None and k_shared.shape[:2] != (slots, cap)):
+        raise ValueError("seq_window_attention_mma: shapes do not match")
+    for t in (q, cache_k, cache_v, k_shared):
+        if t is not None and t.stride(-1) != 1:
+            raise ValueError("seq_window_attention_mma: the last stride must be 1")
+    a = _lib.WindowAttnArgs(q.data_ptr(), q.stride(0), q.stride(1), DK, None, 0, 0, 0,
+                            cache_k.data_ptr(), cache_k.stride(0), cache_k.stride(1), cache_k.stride(2),
+                            cache_v.data_ptr(), cache_v.stride(0), cache_v.stride(1), cache_v.stride(2), DV,
+                            _ptr(sink), gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0,
+                            _ptr(out), _ptr(meta), ntok, H, G, int(window), cap, float(scale))
+    _seq(_lib.load_seq().qspec_seq_window_attention_mma(ctypes.byref(a), k_shared.data_ptr() if k_shared is not None else None,
+                                                        k_shared.stride(0) if k_shared is not None else 0,
+                                                        k_shared.stride(1) if k_shared is not None else 0, DB, int(token_rows), _stream()),
+         "seq_window_attention_mma")
 
 
 def seq_hgrn2(p: torch.Tensor, f_b: torch.Tensor, lower: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, scratch: torch.Tensor,

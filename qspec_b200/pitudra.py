@@ -220,8 +220,9 @@ class _LayerWeights:
             self.dq_norm = small("mix.dq.norm")
             self.dkv_norm = small("mix.dkv.norm") if m.kv_from is None else None
             self.uq = big("mix.uq")
-            self.uk = big("mix.uk").view(m.heads, m.dim, m.kv_rank)                              # q_nope[h] @ uk[h] -> latent space
-            self.uv_t = big("mix.uv").view(m.heads, m.vdim, m.kv_rank).transpose(1, 2)           # latent[h] @ uv_t[h] -> value space
+            self.uk_flat, self.uv_flat = big("mix.uk"), big("mix.uv")                            # latent rows -> per-head keys / values
+            self.uk = self.uk_flat.view(m.heads, m.dim, m.kv_rank)                               # q_nope[h] @ uk[h] -> latent space
+            self.uv_t = self.uv_flat.view(m.heads, m.vdim, m.kv_rank).transpose(1, 2)            # latent[h] @ uv_t[h] -> value space
             self.sink = small("mix.sink")
         elif m.kind == "attention":
             self.qkvg = big("mix.q", "mix.k", "mix.v", "mix.g")                                  # rows [q ; k ; v ; g]
@@ -309,7 +310,7 @@ class PitudraModel(torch.nn.Module):
                                            [m.heads * (2 * m.dim + m.vdim) for m in rec]), **act)
         self.buf_cq = torch.empty(T * mx(m.q_rank for m in lat), **act)
         self.buf_q = torch.empty(T * mx(m.heads * (m.dim + m.rot_dim) for m in lat), **act)
-        self.buf_qa = torch.empty(T * mx([m.heads * m.kv_rank for m in lat] + [m.heads * m.dim for m in att]), **f32)
+        self.buf_qa = torch.empty(T * mx([m.heads * max(m.kv_rank, m.dim + m.rot_dim) for m in lat] + [m.heads * m.dim for m in att]), **f32)
         self.buf_qb = torch.empty(T * mx(m.heads * m.rot_dim for m in lat), **f32)
         self.buf_att = torch.empty(T * mx([m.heads * m.kv_rank for m in lat] + [m.heads * m.vdim for m in att + rec]), **act)
         self.buf_att2 = torch.empty(T * mx(m.heads * m.vdim for m in lat), **act)
@@ -320,9 +321,24 @@ class PitudraModel(torch.nn.Module):
         self.buf_rw = torch.empty(T * tops, **f32)
         self.buf_pair = torch.empty(T * tops * W if moes else 1, **act)
         self.buf_side = torch.empty(T * max(cfg.side_dim, 1), **act)
-        # Steps with several rows per expert take the tensor-core grouped experts (bfloat16); QSPEC_SEQ_TILES=0 keeps the
-        # row-per-CTA form.
+        # bfloat16 takes the tensor-core forms where the sizes allow: grouped experts once an expert sees several rows, window
+        # attention per 16 tokens (prompts) or per group of query heads (decoding). QSPEC_SEQ_TILES=0 keeps the plain forms.
         self.use_tiles = dtype == torch.bfloat16 and os.environ.get("QSPEC_SEQ_TILES", "1") != "0"
+        self.tiles_min_tokens = 64           # a step with fewer tokens, or fewer than 16 per sequence, is decode-shaped
+        # A prompt portion of a latent-attention layer runs in the expanded form: per-head keys and values of the slot's ring
+        # rows from two products (key = [W_uk c | shared rotary part]), which costs a third of the absorbed form's work per
+        # (query, key) pair. Scratch for one slot's ring.
+        lat_tiles = [l.mixer for l in cfg.layers if l.mixer.kind == "latent_attention" and self.use_tiles and
+                     ops.seq_window_attention_mma_supported(dtype, l.mixer.dim, l.mixer.rot_dim, l.mixer.vdim, l.mixer.heads, l.mixer.heads, True)
+                     and l.mixer.kv_rank % 8 == 0 and l.mixer.rot_dim % 8 == 0]
+        caps = {i: c.shape[1] for i, c in self.latent_cache.items()}
+        need_k = mx(caps[i if l.mixer.kv_from is None else l.mixer.kv_from] * l.mixer.heads * l.mixer.dim
+                    for i, l in enumerate(cfg.layers) if l.mixer in lat_tiles)
+        need_v = mx(caps[i if l.mixer.kv_from is None else l.mixer.kv_from] * l.mixer.heads * l.mixer.vdim
+                    for i, l in enumerate(cfg.layers) if l.mixer in lat_tiles)
+        self.buf_kmat = torch.empty(need_k, **act)
+        self.buf_vmat = torch.empty(need_v, **act)
+        self._lat_tiles = {id(m) for m in lat_tiles}
         self._bmm_f32_out = None                       # whether torch.bmm takes bfloat16 operands with a float32 out (probed once)
 
     # ------------------------------------------------------------------------------------------
@@ -360,7 +376,8 @@ class PitudraModel(torch.nn.Module):
             out.copy_(torch.bmm(a, b))
 
     # ------------------------------------------------------------------------------------------
-    def _latent_attention(self, i, m, p, h, tab, T):
+    def _latent_attention(self, i, m, p, h, meta, T, prompt_shaped):
+        tab = meta.table
         own = m.kv_from is None
         ld = m.q_rank + (m.kv_rank + m.rot_dim if own else 0)
         d = self.buf_proj[:T * ld].view(T, ld)
@@ -373,6 +390,22 @@ class PitudraModel(torch.nn.Module):
         H, DQ = m.heads, m.dim + m.rot_dim
         q = self.buf_q[:T * H * DQ].view(T, H, DQ)
         torch.matmul(cq, p.uq.t(), out=q.view(T, H * DQ))
+        if prompt_shaped and len(meta.segments) == 1 and id(m) in self._lat_tiles:
+            # expanded form on the tensor cores: keys and values of every ring row of this sequence's slot
+            slot, cap = meta.segments[0][1], cache.shape[1]
+            ring = cache[slot]
+            kmat = self.buf_kmat[:cap * H * m.dim].view(cap, H * m.dim)
+            vmat = self.buf_vmat[:cap * H * m.vdim].view(cap, H * m.vdim)
+            torch.matmul(ring[:, :m.kv_rank], p.uk_flat.t(), out=kmat)
+            torch.matmul(ring[:, :m.kv_rank], p.uv_flat.t(), out=vmat)
+            qf = self.buf_qa[:T * H * DQ].view(T, H, DQ)
+            qf[:, :, :m.dim].copy_(q[:, :, :m.dim])
+            ops.seq_rotary(q, m.dim, qf[:, :, m.dim:], m.rot_dims, self.inv_freq[i], tab)
+            att = self.buf_att2[:T * H * m.vdim].view(T, H, m.vdim)
+            ops.seq_window_attention_mma(qf, kmat.view(1, cap, H, m.dim).expand(self.n_slots, cap, H, m.dim), cache[:, :, m.kv_rank:],
+                                         vmat.view(1, cap, H, m.vdim).expand(self.n_slots, cap, H, m.vdim), att, tab, m.window, m.scale,
+                                         True, sink=p.sink)
+            return att.view(T, H * m.vdim)
         qa = self.buf_qa[:H * T * m.kv_rank].view(H, T, m.kv_rank)                # W_uk^T q_nope per head, float32
         self._bmm_to_f32(q[:, :, :m.dim].transpose(0, 1), p.uk, qa)
         qb = self.buf_qb[:T * H * m.rot_dim].view(T, H, m.rot_dim)
@@ -384,7 +417,7 @@ class PitudraModel(torch.nn.Module):
         torch.bmm(olat.transpose(0, 1), p.uv_t, out=att.transpose(0, 1))
         return att.view(T, H * m.vdim)
 
-    def _attention(self, i, m, p, h, tab, T):
+    def _attention(self, i, m, p, h, tab, T, prompt_shaped):
         HD, GD, GDV, HDV = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim, m.heads * m.vdim
         ld = HD + GD + GDV + HDV
         proj = self.buf_proj[:T * ld].view(T, ld)
@@ -394,9 +427,13 @@ class PitudraModel(torch.nn.Module):
         ops.seq_qkv_prep(proj, HD, GD, GDV, p.q_norm, p.k_norm, qf, ck, cv, tab, self.cfg.eps)
         att = self.buf_att[:T * HDV].view(T, m.heads, m.vdim)
         cap = ck.shape[1]
-        ops.seq_window_attention(qf.view(T, m.heads, m.dim), None, ck.view(self.n_slots, cap, m.kv_heads, m.dim),
-                                 cv.view(self.n_slots, cap, m.kv_heads, m.vdim), att, tab, m.window, m.scale, sink=p.sink,
-                                 gate=proj[:, HD + GD + GDV:])
+        k4, v4 = ck.view(self.n_slots, cap, m.kv_heads, m.dim), cv.view(self.n_slots, cap, m.kv_heads, m.vdim)
+        gate = proj[:, HD + GD + GDV:]
+        if self.use_tiles and ld % 8 == 0 and ops.seq_window_attention_mma_supported(self.dtype, m.dim, 0, m.vdim, m.heads, m.kv_heads, prompt_shaped):
+            ops.seq_window_attention_mma(qf.view(T, m.heads, m.dim), k4, None, v4, att, tab, m.window, m.scale, prompt_shaped, sink=p.sink,
+                                         gate=gate)
+        else:
+            ops.seq_window_attention(qf.view(T, m.heads, m.dim), None, k4, v4, att, tab, m.window, m.scale, sink=p.sink, gate=gate)
         return att.view(T, HDV)
 
     def _hgrn2(self, i, m, p, h, tab, T):
@@ -419,13 +456,14 @@ class PitudraModel(torch.nn.Module):
         h = self.buf_h[:T * W].view(T, W)
         y = self.buf_y[:T * W].view(T, W)
         ops.seq_embed(self.embed, input_ids, x)
+        prompt_shaped = self.use_tiles and T >= self.tiles_min_tokens and T >= 16 * len(meta.segments)
         for i, spec in enumerate(cfg.layers):
             p, m, f = self.weights[i], spec.mixer, spec.mlp
             ops.seq_token_shift(x, p.shift, self.prev[i], h, tab)
             if m.kind == "latent_attention":
-                att = self._latent_attention(i, m, p, h, tab, T)
+                att = self._latent_attention(i, m, p, h, meta, T, prompt_shaped)
             elif m.kind == "attention":
-                att = self._attention(i, m, p, h, tab, T)
+                att = self._attention(i, m, p, h, tab, T, prompt_shaped)
             else:
                 att = self._hgrn2(i, m, p, h, tab, T)
             torch.matmul(att, p.o.t(), out=y)

@@ -210,6 +210,63 @@ def test_far_key_just_inside_and_just_outside_the_window(dtype):
             assert float(got[inside].min()) > 99 and float(got[outside].abs().max()) < 10
 
 
+@pytest.mark.parametrize("token_rows", [False, True])
+@pytest.mark.parametrize("H,G,DA,DB,DV,window", [(4, 2, 64, 0, 64, 19), (8, 1, 128, 0, 128, 40), (3, 3, 128, 0, 64, 7), (16, 1, 64, 0, 128, 33),
+                                                 (2, 2, 128, 64, 128, 25), (5, 5, 128, 64, 128, 1)])
+def test_window_attention_on_the_tensor_cores(token_rows, H, G, DA, DB, DV, window):
+    """Both row mappings (query heads of a group; 16 consecutive tokens) on batches that mix two sequences: portions that
+    end inside a 16-token block, single tokens, ring wraps, the first tokens. With DB > 0 the last DB entries of every key
+    come from a part shared by all heads."""
+    _cuda()
+    from qspec_b200 import ops
+    if not ops.seq_window_attention_mma_supported(BF16, DA, DB, DV, H, G, token_rows):
+        pytest.skip("shape not taken by this row mapping")
+    g = torch.Generator().manual_seed(H + DA + window)
+    lens, scale, step_cap = (61, 45), 0.2, 24
+    cap = window - 1 + step_cap
+    seqs = []
+    for n in lens:
+        q, k, v = rnd(g, n, H, DA + DB, dtype=BF16), rnd(g, n, G, DA, dtype=BF16), rnd(g, n, G, DV, dtype=BF16)
+        ks = rnd(g, n, DB, dtype=BF16) if DB else None
+        kfull = k if not DB else torch.cat([k, ks[:, None, :].expand(n, G, DB)], -1)
+        seqs.append((q, k, ks, v, kfull))
+    sink = rnd(g, H)
+    gate = [rnd(g, n, H * DV, dtype=BF16) for n in lens]
+    want = [_plain_window_attention(q, kf, v, sink, window, scale, G) * torch.sigmoid(gt.view(n, H, DV))
+            for (q, k, ks, v, kf), gt, n in zip(seqs, gate, lens)]
+    ck = torch.full((4, cap, G, DA), 1e4, dtype=BF16, device="cuda")
+    cs = torch.full((4, cap, max(DB, 8)), 1e4, dtype=BF16, device="cuda")
+    cv = torch.full((4, cap, G, DV), 1e4, dtype=BF16, device="cuda")
+    slots, at = (3, 1), [0, 0]
+    got = [[], []]
+    plan = [(20, 5), (1, 1), (24, 23), (3, 0), (13, 16)]
+    for step in plan:
+        segs, qs, gs = [], [], []
+        for b, n in enumerate(step):
+            if not n:
+                continue
+            q, k, ks, v, _ = seqs[b]
+            for t in range(at[b], at[b] + n):
+                ck[slots[b], t % cap] = k[t].to(BF16).cuda()
+                cv[slots[b], t % cap] = v[t].to(BF16).cuda()
+                if DB:
+                    cs[slots[b], t % cap, :DB] = ks[t].to(BF16).cuda()
+            segs.append((slots[b], at[b], n, 0))
+            qs.append(q[at[b]:at[b] + n]); gs.append(gate[b][at[b]:at[b] + n])
+        ntok = sum(n for n in step)
+        out = torch.empty(ntok, H, DV, dtype=BF16, device="cuda")
+        ops.seq_window_attention_mma(torch.cat(qs).float().cuda(), ck, cs[:, :, :DB] if DB else None, cv, out, meta_table(segs), window, scale,
+                                     token_rows, sink=sink.float().cuda(), gate=torch.cat(gs).to(BF16).cuda())
+        o = 0
+        for b, n in enumerate(step):
+            got[b].append(out[o:o + n].float().cpu())
+            o += n
+            at[b] += n
+    assert at == list(lens)
+    for b in range(2):
+        close(torch.cat(got[b]), want[b], BF16)
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_the_sink_counts_once_unscaled_and_holds_no_value(dtype):
     """A query whose scores are all zero: with sink s and n visible keys every key weighs 1 / (n + e^s)."""
@@ -357,6 +414,11 @@ CONFIGS = {
     "wide": config([dict(recurrent(heads=4, dim=16, vdim=16), mlp=moe(ff=32, experts=2, top=2)),
                     dict(latent(heads=4, dim=16, vdim=16, rot_dim=8, q_rank=32, kv_rank=24, window=500), mlp=moe(ff=32, experts=2, top=2)),
                     dict(attention(heads=4, kv=4, dim=16, vdim=16, window=300), mlp=moe(ff=32, experts=2, top=2))], width=64, side=3),
+    # head sizes that the tensor-core attention forms take in bfloat16 (prompts of a latent layer run in the expanded form)
+    "tiles": config([dict(latent(heads=2, dim=128, vdim=128, rot_dim=64, q_rank=24, kv_rank=32, window=21, scale=0.08), mlp=moe()),
+                     dict(attention(heads=4, kv=2, dim=64, vdim=64, window=30, scale=0.12), mlp=moe()),
+                     dict(latent(heads=2, dim=128, vdim=128, rot_dim=64, q_rank=24, kv_rank=32, window=70, scale=0.08, kv_from=0), mlp=None),
+                     dict(attention(heads=2, kv=1, dim=128, vdim=128, window=9, scale=0.09), mlp=None)], width=64, side=4),
 }
 
 
@@ -469,6 +531,20 @@ def test_mixed_batches_equal_each_request_alone_and_slots_are_reused(dtype):
     assert fed == lens and not live
     for r in toks:
         close_logits(torch.cat(got[r]), ref[r], dtype)
+
+
+def test_prompt_and_decode_forms_on_the_tensor_cores_match_the_plain_implementation():
+    """bfloat16 steps of 64 tokens and more take the 16-token form (and the expanded latent form), shorter ones the
+    head-row form; both against the plain implementation, with a portion that continues a sequence."""
+    cfg, w, model, s = build("tiles", BF16, max_step_tokens=128)
+    toks = tokens(150, cfg["vocab"], 3)
+    ref = O.forward(cfg, w, toks)
+    rows = [s.feed([("a", toks[:70], list(range(70)))]), s.feed([("a", toks[70:75], list(range(5)))]),
+            s.feed([("a", toks[75:], list(range(75)))])]
+    close_logits(torch.cat(rows), ref, BF16)
+    s.release("a")
+    rows = [s.feed([("b", toks[:40], list(range(40)))])] + [s.feed([("b", [t], [0])]) for t in toks[40:90]]
+    close_logits(torch.cat(rows), ref[:90], BF16)
 
 
 def test_batch_composition_changes_nothing_in_float32():
