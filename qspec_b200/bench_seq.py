@@ -389,12 +389,40 @@ def _pitudra_kernel_table(torch, s, hbm_gbs, bf16_tflops):
         def lat_attn(i):
             c = lat_cache[i % 2].unsqueeze(2)
             ops.seq_window_attention(qa[i % 2].transpose(0, 1), qb, c, c[..., :kvr], olat, tab, win, 0.07, sink=sink)
-        us = _time_us(torch, [lambda i=i: lat_attn(i) for i in range(2)], reps=6 if label == "prompt" else 20)
         if label == "prompt":
-            add("seq_window_attention, latent form", f"T={T} window={win} H={H} key {kvr}+{rot} value {kvr}", us,
-                flops=2.0 * visible * H * (2 * kvr + rot), note="one CTA per (token, head), float32 lanes: no tensor cores yet")
+            # prompts run the expanded form: per-head keys / values of one slot's ring rows from two products, then tiles
+            wuk = (torch.randn(H * D, kvr, device=dev) * kvr ** -0.5).to(bf)
+            wuv = (torch.randn(H * D, kvr, device=dev) * kvr ** -0.5).to(bf)
+            kmat = torch.empty(cap, H * D, device=dev, dtype=bf)
+            vmat = torch.empty(cap, H * D, device=dev, dtype=bf)
+
+            def expand(i):
+                ring = lat_cache[i % 2][0]
+                torch.matmul(ring[:, :kvr], wuk.t(), out=kmat)
+                torch.matmul(ring[:, :kvr], wuv.t(), out=vmat)
+            us = _time_us(torch, [lambda i=i: expand(i) for i in range(2)])
+            add("latent keys / values of a slot's ring rows (2 vendor products)", f"{cap}x{H * D}x{kvr} x 2", us, flops=4.0 * cap * H * D * kvr)
+            qfull = [torch.randn(T, H, D + rot, device=dev) * 0.3 for _ in range(2)]
+            oexp = torch.empty(T, H, D, device=dev, dtype=bf)
+            us = _time_us(torch, [lambda i=i: ops.seq_window_attention_mma(
+                qfull[i % 2], kmat.view(1, cap, H, D).expand(nslots, cap, H, D), lat_cache[i % 2][:, :, kvr:],
+                vmat.view(1, cap, H, D).expand(nslots, cap, H, D), oexp, tab, win, 0.07, True, sink=sink) for i in range(2)])
+            add("seq_window_attention_mma, latent expanded form (16 tokens per CTA)", f"T={T} window={win} H={H} key {D}+{rot} value {D}", us,
+                flops=2.0 * visible * H * (2 * D + rot))
         else:
-            add("seq_window_attention, latent form", f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * (kvr + rot) * 2)
+            us = _time_us(torch, [lambda i=i: lat_attn(i) for i in range(2)])
+            add("seq_window_attention, latent absorbed form (CUDA cores; float32 and odd sizes)", f"64 seqs x 1, {visible // 64} keys each", us,
+                nbytes=visible * (kvr + rot) * 2)
+            qabs = [torch.randn(T, H, kvr + rot, device=dev) * 0.05 for _ in range(2)]
+            groups = 1 if H <= 16 else H // 16
+
+            def lat_mma(i):
+                c = lat_cache[i % 2]
+                k4 = c[:, :, :kvr].unsqueeze(2).expand(nslots, cap, groups, kvr)
+                ops.seq_window_attention_mma(qabs[i % 2], k4, c[:, :, kvr:], k4, olat, tab, win, 0.07, False, sink=sink)
+            us = _time_us(torch, [lambda i=i: lat_mma(i) for i in range(2)])
+            add("seq_window_attention_mma, latent absorbed form (16 heads per CTA, values in 128-column slices)",
+                f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * (kvr + rot) * 2)
         # grouped-query attention
         ldq = H * D + 2 * G * D + H * D
         pq = [(torch.randn(T, ldq, device=dev) * 0.3).to(bf) for _ in range(nbuf)]
@@ -405,15 +433,19 @@ def _pitudra_kernel_table(torch, s, hbm_gbs, bf16_tflops):
         add("seq_qkv_prep (2 norms + cache rows)", f"{label} T={T}", us, nbytes=T * ((H + 2 * G) * D * 2 + H * D * 4 + 2 * G * D * 2))
         att = torch.empty(T, H, D, device=dev, dtype=bf)
 
+        k4 = [c.view(nslots, cap, G, D) for c in ck]
+        v4 = [c.view(nslots, cap, G, D) for c in cv]
+
         def gqa(i):
-            ops.seq_window_attention(qf[i % 2].view(T, H, D), None, ck[i % 2].view(nslots, cap, G, D), cv[i % 2].view(nslots, cap, G, D), att,
-                                     tab, win, D ** -0.5, sink=sink, gate=pq[i % nbuf][:, H * D + 2 * G * D:])
-        us = _time_us(torch, [lambda i=i: gqa(i) for i in range(2)], reps=6 if label == "prompt" else 20)
+            ops.seq_window_attention_mma(qf[i % 2].view(T, H, D), k4[i % 2], None, v4[i % 2], att, tab, win, D ** -0.5, label == "prompt",
+                                         sink=sink, gate=pq[i % nbuf][:, H * D + 2 * G * D:])
+        us = _time_us(torch, [lambda i=i: gqa(i) for i in range(2)])
         if label == "prompt":
-            add("seq_window_attention, grouped-query form + gate", f"T={T} window={win} H={H} G={G} D={D}", us, flops=2.0 * visible * H * 2 * D,
-                note="one CTA per (token, head), float32 lanes: no tensor cores yet")
+            add("seq_window_attention_mma, grouped-query form + gate (16 tokens per CTA)", f"T={T} window={win} H={H} G={G} D={D}", us,
+                flops=2.0 * visible * H * 2 * D)
         else:
-            add("seq_window_attention, grouped-query form + gate", f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * G * 2 * D * 2)
+            add("seq_window_attention_mma, grouped-query form + gate (heads of a group per CTA)", f"64 seqs x 1, {visible // 64} keys each", us,
+                nbytes=visible * G * 2 * D * 2)
         # recurrence
         ldr = H * 3 * D
         pr = [(torch.randn(T, ldr, device=dev)).to(bf) for _ in range(nbuf)]

@@ -183,8 +183,8 @@ qkv_prep_kernel(const T* __restrict__ p, int ld, int HD, int GD, int GDV, const 
 // key[DA:DA+DB]); keys and values are rows of a per-slot ring (row = position % cap) that already holds the step's
 // own tokens. A warp takes every fourth run of four keys of the window: lanes along the rows for the dot products, an
 // online softmax per warp, and the four partial results are merged in shared memory together with the sink term
-// exp(sink[h]) of the denominator. Which warp takes which key depends on the token's position only, so a token's result does not depend
-// on how its sequence was cut into steps or on its neighbours in the batch.
+// exp(sink[h]) of the denominator. Which warp takes which key depends on the token's position only, so a token's result
+// does not depend on how its sequence was cut into steps or on its neighbours in the batch.
 template <typename T, int NACC, int VEC>
 __global__ void __launch_bounds__(128)
 window_attn_kernel(const float* __restrict__ qa, long long qa_ts, long long qa_hs, int DA, const float* __restrict__ qb,
@@ -312,7 +312,8 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b
   const TokMeta mt = load_meta(meta, ntok, i);
   if (i != mt.seg_begin) return;
   constexpr int BT = 8, DP = 8 * NS, R = (BT * DP) / 256;      // tokens per block, padded rows, staged values per thread
-  __shared__ float sq[BT][DP], sf[BT][DP], sg[BT][DP], sv[BT][32], spart[BT][8][32];
+  __shared__ __align__(16) float sq[BT][DP], sf[BT][DP], sg[BT][DP];
+  __shared__ float sv[BT][32], spart[BT][8][32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int col = v0 + lane;
   const bool live = col < DV;
@@ -358,13 +359,19 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b
     const int nb = min(BT, mt.seg_end - tb);
     for (int tt = 0; tt < nb; ++tt) {
       const float v = sv[tt][lane];
-      float part = 0.f;
+      float p0 = 0.f, p1 = 0.f;                             // two chains: the sum over rows is the long dependency
+      const float4* f4 = reinterpret_cast<const float4*>(&sf[tt][d0]);
+      const float4* g4 = reinterpret_cast<const float4*>(&sg[tt][d0]);
+      const float4* q4 = reinterpret_cast<const float4*>(&sq[tt][d0]);
 #pragma unroll
-      for (int k = 0; k < NS; ++k) {
-        S[k] = sf[tt][d0 + k] * S[k] + sg[tt][d0 + k] * v;
-        part += S[k] * sq[tt][d0 + k];
+      for (int k = 0; k < NS / 4; ++k) {
+        const float4 f = f4[k], gq = g4[k], q = q4[k];
+        S[4 * k] = f.x * S[4 * k] + gq.x * v;             p0 += S[4 * k] * q.x;
+        S[4 * k + 1] = f.y * S[4 * k + 1] + gq.y * v;     p1 += S[4 * k + 1] * q.y;
+        S[4 * k + 2] = f.z * S[4 * k + 2] + gq.z * v;     p0 += S[4 * k + 2] * q.z;
+        S[4 * k + 3] = f.w * S[4 * k + 3] + gq.w * v;     p1 += S[4 * k + 3] * q.w;
       }
-      spart[tt][warp][lane] = part;
+      spart[tt][warp][lane] = p0 + p1;
     }
     __syncthreads();
     if (warp < nb && live) {

@@ -972,10 +972,12 @@ struct WinMma {
   const bf16* kB; long long kB_ss; int kB_rs;
   const bf16* v; long long v_ss; int v_rs, v_hs;
   const float* sink; const bf16* gate; int gate_ld;
-  bf16* out; const int* meta; int ntok, H, G, window, cap; float scale; int token_rows;
+  bf16* out; int out_hs; const int* meta; int ntok, H, G, window, cap; float scale; int token_rows;
 };
 
-template <int DA, int DB, int DV>
+// STREAM: key rows are loaded inside the product loop instead of a whole step ahead (long keys: the fragments of a step
+// would not fit the register file); blockIdx.z selects a slice of DV value columns (values longer than DV).
+template <int DA, int DB, int DV, bool STREAM>
 __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a) {
   pdl_enter();
   constexpr int DK = DA + DB, QS = DK / 2 + 4;
@@ -1014,7 +1016,7 @@ __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a)
   for (int t = 0; t < DV / 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
   float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-  struct Rows { uint4 k[2][DK / 32]; uint4 v[4][DV / 64]; };
+  struct Rows { uint4 k[2][STREAM ? 1 : DK / 32]; uint4 v[4][DV / 64]; };
 
   int r0 = 0;
   while (r0 < 16 && s_tok[r0] >= 0) {
@@ -1027,7 +1029,7 @@ __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a)
     const int nkeys = pmax - jlo + 1;
     const bf16* kA = a.kA + (size_t)slot * a.kA_ss + (size_t)kvh * a.kA_hs;
     const bf16* kB = DB ? a.kB + (size_t)slot * a.kB_ss : nullptr;
-    const bf16* vb = a.v + (size_t)slot * a.v_ss + (size_t)kvh * a.v_hs;
+    const bf16* vb = a.v + (size_t)slot * a.v_ss + (size_t)kvh * a.v_hs + (size_t)blockIdx.z * DV;
     auto fetch = [&](int hb, Rows& r) {
       const int kb = hb * 16;
 #pragma unroll
@@ -1057,23 +1059,59 @@ __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a)
     const bool inB = a.token_rows ? (segB == seg && s_tok[rB] >= 0) : rB < rep;
     Rows cur, nxt;
     int hb = warp;
-    if (hb * 16 < nkeys) fetch(hb, cur);
+    if (!STREAM && hb * 16 < nkeys) fetch(hb, cur);
     for (; hb * 16 < nkeys; hb += 4) {
       const int kb = hb * 16;
-      if ((hb + 4) * 16 < nkeys) fetch(hb + 4, nxt);
+      if (!STREAM && (hb + 4) * 16 < nkeys) fetch(hb + 4, nxt);
       float s[2][4];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      if (STREAM) {
+        const bf16* kp[2];
+        const bf16* kq[2];
+        bool okk[2];
 #pragma unroll
-      for (int j = 0; j < DK / 32; ++j)
+        for (int nt = 0; nt < 2; ++nt) {
+          const int jj = kb + 8 * nt + gid;
+          okk[nt] = jj < nkeys;
+          const int row = okk[nt] ? (jlo + jj) % a.cap : 0;
+          kp[nt] = kA + (size_t)row * a.kA_rs + 8 * tig;
+          kq[nt] = DB ? kB + (size_t)row * a.kB_rs + 8 * tig : nullptr;
+        }
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int wq = 16 * j + 4 * tig + 2 * half;
-          const uint32_t af[4] = {sQ[gid * QS + wq], sQ[(gid + 8) * QS + wq], sQ[gid * QS + wq + 1], sQ[(gid + 8) * QS + wq + 1]};
+        for (int j = 0; j < DK / 32; ++j) {
+          uint4 kk[2];
 #pragma unroll
           for (int nt = 0; nt < 2; ++nt)
-            mma_bf16_16816(s[nt], af, half ? cur.k[nt][j].z : cur.k[nt][j].x, half ? cur.k[nt][j].w : cur.k[nt][j].y);
+            kk[nt] = !okk[nt] ? zero4 : __ldg(reinterpret_cast<const uint4*>(j < DA / 32 ? kp[nt] + 32 * j : kq[nt] + 32 * (j - DA / 32)));
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int wq = 16 * j + 4 * tig + 2 * half;
+            const uint32_t af[4] = {sQ[gid * QS + wq], sQ[(gid + 8) * QS + wq], sQ[gid * QS + wq + 1], sQ[(gid + 8) * QS + wq + 1]};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) mma_bf16_16816(s[nt], af, half ? kk[nt].z : kk[nt].x, half ? kk[nt].w : kk[nt].y);
+          }
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {                       // this step's value rows, in flight during the softmax
+          const int jj = kb + 2 * tig + (q & 1) + 8 * (q >> 1);
+          const bool ok = jj < nkeys;
+          const bf16* vp = vb + (size_t)(ok ? (jlo + jj) % a.cap : 0) * a.v_rs;
+#pragma unroll
+          for (int sp = 0; sp < DV / 64; ++sp) cur.v[q][sp] = ok ? __ldg(reinterpret_cast<const uint4*>(vp + 64 * sp + 8 * gid)) : zero4;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < DK / 32; ++j)
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int wq = 16 * j + 4 * tig + 2 * half;
+            const uint32_t af[4] = {sQ[gid * QS + wq], sQ[(gid + 8) * QS + wq], sQ[gid * QS + wq + 1], sQ[(gid + 8) * QS + wq + 1]};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+              mma_bf16_16816(s[nt], af, half ? cur.k[nt][j].z : cur.k[nt][j].x, half ? cur.k[nt][j].w : cur.k[nt][j].y);
+          }
+      }
       // visible: same sequence, key position <= the row's and within its window
       float mxA = -INFINITY, mxB = -INFINITY;
 #pragma unroll
@@ -1120,7 +1158,7 @@ __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a)
           mma_bf16_16816(o[sp * 8 + t], al, b0, b1);
         }
       }
-      cur = nxt;
+      if (!STREAM) cur = nxt;
     }
     if (!a.token_rows) break;
     r0 = r1;
@@ -1154,31 +1192,40 @@ __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a)
       acc += sO[(w * 16 + row) * DV + d] * f;
     }
     float r = acc / L;
-    if (a.gate) r *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(a.gate[(size_t)tok * a.gate_ld + (size_t)head * DV + d])));
-    a.out[((size_t)tok * a.H + head) * DV + d] = __float2bfloat16_rn(r);
+    if (a.gate) r *= __fdividef(1.0f, 1.0f + __expf(-__bfloat162float(a.gate[(size_t)tok * a.gate_ld + (size_t)head * a.out_hs + (size_t)blockIdx.z * DV + d])));
+    a.out[((size_t)tok * a.H + head) * a.out_hs + (size_t)blockIdx.z * DV + d] = __float2bfloat16_rn(r);
   }
 }
 
-template <int DA, int DB, int DV>
-static int launch_window_mma(const WinMma& a, cudaStream_t st) {
+template <int DA, int DB, int DV, bool STREAM>
+static int launch_window_mma(const WinMma& a, int slices, cudaStream_t st) {
   constexpr size_t smem = (size_t)16 * ((DA + DB) / 2 + 4) * 4 + (size_t)4 * 16 * DV * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    QSPEC_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<DA, DB, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    QSPEC_CUDA(cudaFuncSetAttribute(window_attn_mma_kernel<DA, DB, DV, STREAM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  const dim3 grid = a.token_rows ? dim3((a.ntok + 15) / 16, a.H) : dim3(a.ntok, a.G);
-  launch_pdl(window_attn_mma_kernel<DA, DB, DV>, grid, dim3(128), smem, st, a);
+  const dim3 grid = a.token_rows ? dim3((a.ntok + 15) / 16, a.H, slices) : dim3(a.ntok, a.G, slices);
+  launch_pdl(window_attn_mma_kernel<DA, DB, DV, STREAM>, grid, dim3(128), smem, st, a);
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
 
-// Entry for qspec_seq_window_attention_mma (below) and for seq_mix_kernels.cu: -1 when the shape is not one this form takes.
+// Shapes: per-head key part 64 or 128 with values of 64 or 128; 128 + a shared part of 64 with values of 128 (a latent
+// layer's expanded form); 256 or 512 + a shared part of 64 with values of 128, 256, 384 or 512 in slices of 128 columns (a
+// latent cache read in the absorbed form: key and value are the same rows).
+bool window_mma_shape(int DA, int DB, int DV) {
+  if (DB == 0) return (DA == 64 || DA == 128) && (DV == 64 || DV == 128);
+  if (DB != 64) return false;
+  if (DA == 128) return DV == 128;
+  return (DA == 256 || DA == 512) && DV % 128 == 0 && DV >= 128 && DV <= 512;
+}
+
+// Entry for qspec_seq_window_attention_mma (below): -1 when the shape is not one this form takes.
 int window_attention_mma(const qspec_window_attn_args* p, const void* kB, long long kB_ss, int kB_rs, int DB, int token_rows,
                          cudaStream_t st) {
   const int DA = p->DA, DV = p->DV;
-  const bool shape = (DB == 0 && (DA == 64 || DA == 128) && (DV == 64 || DV == 128)) || (DA == 128 && DB == 64 && DV == 128);
-  const bool ok = shape && p->H % p->G == 0 && (token_rows || p->H / p->G <= 16) && p->H <= 65535 && p->G <= 65535 &&
+  const bool ok = window_mma_shape(DA, DB, DV) && p->H % p->G == 0 && (token_rows || p->H / p->G <= 16) && p->H <= 65535 && p->G <= 65535 &&
                   p->k_row_stride % 8 == 0 && p->k_head_stride % 8 == 0 && p->k_slot_stride % 8 == 0 && p->v_row_stride % 8 == 0 &&
                   p->v_head_stride % 8 == 0 && p->v_slot_stride % 8 == 0 && kB_rs % 8 == 0 && kB_ss % 8 == 0 &&
                   p->qa_tok_stride % 2 == 0 && p->qa_head_stride % 2 == 0 &&
@@ -1190,13 +1237,15 @@ int window_attention_mma(const qspec_window_attn_args* p, const void* kB, long l
   a.kB = (const bf16*)kB; a.kB_ss = kB_ss; a.kB_rs = kB_rs;
   a.v = (const bf16*)p->v; a.v_ss = p->v_slot_stride; a.v_rs = p->v_row_stride; a.v_hs = p->v_head_stride;
   a.sink = p->sink; a.gate = (const bf16*)p->gate; a.gate_ld = p->gate_ld;
-  a.out = (bf16*)p->out; a.meta = p->meta; a.ntok = p->ntok; a.H = p->H; a.G = p->G; a.window = p->window; a.cap = p->cap;
+  a.out = (bf16*)p->out; a.out_hs = DV; a.meta = p->meta; a.ntok = p->ntok; a.H = p->H; a.G = p->G; a.window = p->window; a.cap = p->cap;
   a.scale = p->scale; a.token_rows = token_rows;
-  if (DB) return launch_window_mma<128, 64, 128>(a, st);
-  if (DA == 64 && DV == 64) return launch_window_mma<64, 0, 64>(a, st);
-  if (DA == 64) return launch_window_mma<64, 0, 128>(a, st);
-  if (DV == 64) return launch_window_mma<128, 0, 64>(a, st);
-  return launch_window_mma<128, 0, 128>(a, st);
+  if (DA == 512) return launch_window_mma<512, 64, 128, true>(a, DV / 128, st);
+  if (DA == 256) return launch_window_mma<256, 64, 128, true>(a, DV / 128, st);
+  if (DB) return launch_window_mma<128, 64, 128, false>(a, 1, st);
+  if (DA == 64 && DV == 64) return launch_window_mma<64, 0, 64, false>(a, 1, st);
+  if (DA == 64) return launch_window_mma<64, 0, 128, false>(a, 1, st);
+  if (DV == 64) return launch_window_mma<128, 0, 64, false>(a, 1, st);
+  return launch_window_mma<128, 0, 128, false>(a, 1, st);
 }
 }  // namespace qspec
 
@@ -1215,6 +1264,5 @@ extern "C" int qspec_seq_window_attention_mma(const qspec_window_attn_args* args
 }
 
 extern "C" int qspec_seq_window_attention_mma_supported(int DA, int DB, int DV, int H, int G, int token_rows) {
-  const bool shape = (DB == 0 && (DA == 64 || DA == 128) && (DV == 64 || DV == 128)) || (DA == 128 && DB == 64 && DV == 128);
-  return shape && G > 0 && H % G == 0 && (token_rows || H / G <= 16);
+  return qspec::window_mma_shape(DA, DB, DV) && G > 0 && H % G == 0 && (token_rows || H / G <= 16);
 }

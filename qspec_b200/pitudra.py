@@ -310,8 +310,7 @@ class PitudraModel(torch.nn.Module):
                                            [m.heads * (2 * m.dim + m.vdim) for m in rec]), **act)
         self.buf_cq = torch.empty(T * mx(m.q_rank for m in lat), **act)
         self.buf_q = torch.empty(T * mx(m.heads * (m.dim + m.rot_dim) for m in lat), **act)
-        self.buf_qa = torch.empty(T * mx([m.heads * max(m.kv_rank, m.dim + m.rot_dim) for m in lat] + [m.heads * m.dim for m in att]), **f32)
-        self.buf_qb = torch.empty(T * mx(m.heads * m.rot_dim for m in lat), **f32)
+        self.buf_qa = torch.empty(T * mx([m.heads * (max(m.kv_rank, m.dim) + m.rot_dim) for m in lat] + [m.heads * m.dim for m in att]), **f32)
         self.buf_att = torch.empty(T * mx([m.heads * m.kv_rank for m in lat] + [m.heads * m.vdim for m in att + rec]), **act)
         self.buf_att2 = torch.empty(T * mx(m.heads * m.vdim for m in lat), **act)
         self.buf_rec = torch.empty(T * mx(m.heads * m.vdim for m in rec), **f32)
@@ -406,13 +405,21 @@ class PitudraModel(torch.nn.Module):
                                          vmat.view(1, cap, H, m.vdim).expand(self.n_slots, cap, H, m.vdim), att, tab, m.window, m.scale,
                                          True, sink=p.sink)
             return att.view(T, H * m.vdim)
-        qa = self.buf_qa[:H * T * m.kv_rank].view(H, T, m.kv_rank)                # W_uk^T q_nope per head, float32
-        self._bmm_to_f32(q[:, :, :m.dim].transpose(0, 1), p.uk, qa)
-        qb = self.buf_qb[:T * H * m.rot_dim].view(T, H, m.rot_dim)
-        ops.seq_rotary(q, m.dim, qb, m.rot_dims, self.inv_freq[i], tab)
-        olat = self.buf_att[:T * H * m.kv_rank].view(T, H, m.kv_rank)
-        ck = cache.unsqueeze(2)                                                     # one key/value head: [slots, cap, 1, kv_rank + rot_dim]
-        ops.seq_window_attention(qa.transpose(0, 1), qb, ck, ck[..., :m.kv_rank], olat, tab, m.window, m.scale, sink=p.sink)
+        # absorbed form: the query moves into the latent space (W_uk^T q_nope per head, float32) and the cache rows serve as
+        # keys and as values; the up-projection of the values follows the attention
+        r, R = m.kv_rank, m.rot_dim
+        qf = self.buf_qa[:T * H * (r + R)].view(T, H, r + R)
+        self._bmm_to_f32(q[:, :, :m.dim].transpose(0, 1), p.uk, qf[:, :, :r].transpose(0, 1))
+        ops.seq_rotary(q, m.dim, qf[:, :, r:], m.rot_dims, self.inv_freq[i], tab)
+        olat = self.buf_att[:T * H * r].view(T, H, r)
+        groups = 1 if H <= 16 else (H // 16 if H % 16 == 0 else 0)                 # the heads share one key row: 16 of them per CTA
+        if self.use_tiles and groups and r % 8 == 0 and R % 8 == 0 and \
+                ops.seq_window_attention_mma_supported(self.dtype, r, R, r, H, groups, False):
+            ck = cache[:, :, :r].unsqueeze(2).expand(cache.shape[0], cache.shape[1], groups, r)
+            ops.seq_window_attention_mma(qf, ck, cache[:, :, r:], ck, olat, tab, m.window, m.scale, False, sink=p.sink)
+        else:
+            ck = cache.unsqueeze(2)                                                 # one key/value head: [slots, cap, 1, kv_rank + rot_dim]
+            ops.seq_window_attention(qf[:, :, :r], qf[:, :, r:], ck, ck[..., :r], olat, tab, m.window, m.scale, sink=p.sink)
         att = self.buf_att2[:T * H * m.vdim].view(T, H, m.vdim)
         torch.bmm(olat.transpose(0, 1), p.uv_t, out=att.transpose(0, 1))
         return att.view(T, H * m.vdim)

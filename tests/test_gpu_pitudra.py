@@ -267,6 +267,32 @@ def test_window_attention_on_the_tensor_cores(token_rows, H, G, DA, DB, DV, wind
         close(torch.cat(got[b]), want[b], BF16)
 
 
+@pytest.mark.parametrize("H,groups,r,R,window", [(16, 1, 256, 64, 37), (32, 2, 512, 64, 20), (5, 1, 256, 64, 1), (3, 1, 512, 64, 70)])
+def test_absorbed_latent_attention_on_the_tensor_cores(H, groups, r, R, window):
+    """The cache rows are keys and values at once ([latent | shared rotary part], value = the latent); all heads read the same
+    rows, 16 heads per CTA, the values in slices of 128 columns. Decoded token by token and in small portions."""
+    _cuda()
+    from qspec_b200 import ops
+    g = torch.Generator().manual_seed(H + r)
+    n, scale, step_cap = 90, 0.05, 8
+    cap = window - 1 + step_cap
+    q, c = rnd(g, n, H, r + R, dtype=BF16), rnd(g, n, 1, r + R, dtype=BF16)
+    sink = rnd(g, H)
+    want = _plain_window_attention(q, c, c[..., :r], sink, window, scale, 1)
+    cache = torch.full((3, cap, r + R), 1e4, dtype=BF16, device="cuda")
+    at, got = 0, []
+    for k in [1] * 40 + [5, 8, 3, 8, 8, 2, 8, 8]:
+        cache[2, [(t % cap) for t in range(at, at + k)]] = c[at:at + k, 0].to(BF16).cuda()
+        out = torch.empty(k, H, r, dtype=BF16, device="cuda")
+        ck = cache[:, :, :r].unsqueeze(2).expand(3, cap, groups, r)
+        ops.seq_window_attention_mma(q[at:at + k].float().cuda(), ck, cache[:, :, r:], ck, out, meta_table([(2, at, k, 0)]), window, scale,
+                                     False, sink=sink.float().cuda())
+        got.append(out.float().cpu())
+        at += k
+    assert at == n
+    close(torch.cat(got), want, BF16)
+
+
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_the_sink_counts_once_unscaled_and_holds_no_value(dtype):
     """A query whose scores are all zero: with sink s and n visible keys every key weighs 1 / (n + e^s)."""
@@ -414,6 +440,10 @@ CONFIGS = {
     "wide": config([dict(recurrent(heads=4, dim=16, vdim=16), mlp=moe(ff=32, experts=2, top=2)),
                     dict(latent(heads=4, dim=16, vdim=16, rot_dim=8, q_rank=32, kv_rank=24, window=500), mlp=moe(ff=32, experts=2, top=2)),
                     dict(attention(heads=4, kv=4, dim=16, vdim=16, window=300), mlp=moe(ff=32, experts=2, top=2))], width=64, side=3),
+    # a latent cache wide enough for the tensor-core absorbed form in bfloat16 decoding; the borrowing layer has other heads
+    "latent256": config([dict(latent(heads=2, dim=8, vdim=8, rot_dim=64, q_rank=16, kv_rank=256, window=11, scale=0.1), mlp=moe()),
+                         dict(latent(heads=3, dim=16, vdim=4, rot_dim=64, q_rank=8, kv_rank=256, window=30, scale=0.1, kv_from=0), mlp=None)],
+                        width=48, side=0),
     # head sizes that the tensor-core attention forms take in bfloat16 (prompts of a latent layer run in the expanded form)
     "tiles": config([dict(latent(heads=2, dim=128, vdim=128, rot_dim=64, q_rank=24, kv_rank=32, window=21, scale=0.08), mlp=moe()),
                      dict(attention(heads=4, kv=2, dim=64, vdim=64, window=30, scale=0.12), mlp=moe()),
