@@ -188,10 +188,11 @@ int qspec_seq_window_attention_mma_supported(int DA, int DB, int DV, int H, int 
 /* HGRN2 recurrence. Row t of p = [zq (H x D) | zf (H x D) | v (H x DV)]. q = silu(zq), f = lower + (1 - lower) *
  * sigmoid(zf + f_b); per head S <- diag(f) S + (1 - f) v^T, o = S^T q; out[t, h] = unit_rms(o over DV) * norm_w.
  * state: float32 [slots, H, D, DV], read at a segment's start (zero at position 0), written at its end.
- * scratch: float32 [ntok, H * DV]. D <= 256. */
+ * scratch: float32 [ntok, H * DV]. D <= 256. seg_starts (may be NULL): int32 [nseg], the batch row of every segment's
+ * first token; with it the grid has one CTA per segment instead of one per token. */
 int qspec_seq_hgrn2(const void* p, int ld, const float* f_b, const float* lower, const float* norm_w, float* state,
-                    float* scratch, void* out, const int* meta, int ntok, int H, int D, int DV, float eps, int dtype,
-                    void* stream);
+                    float* scratch, void* out, const int* meta, const int* seg_starts, int nseg, int ntok, int H, int D, int DV,
+                    float eps, int dtype, void* stream);
 
 /* g[t, :] <- gelu_tanh(g[t, :]) * table[ids[t], col0 : col0 + sd]  (g [ntok, sd], table [V, table_ld]). */
 int qspec_seq_side_gate(void* g, const void* table, const int* ids, int col0, int sd, int table_ld, int V, int ntok, int dtype,

@@ -146,8 +146,8 @@ SEQ_SIGNATURES = {
     "qspec_seq_window_attention": (c_int, [c_void_p, c_int, c_void_p]),
     "qspec_seq_window_attention_mma": (c_int, [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]),
     "qspec_seq_window_attention_mma_supported": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
-    "qspec_seq_hgrn2": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                c_int, c_int, c_float, c_int, c_void_p]),
+    "qspec_seq_hgrn2": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "qspec_seq_side_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
 }
 

@@ -297,33 +297,36 @@ window_attn_kernel(const float* __restrict__ qa, long long qa_ts, long long qa_h
 
 // ---- HGRN2: gated linear recurrence ---------------------------------------------------------------------------------
 // Per head S <- diag(f) S + (1 - f) v^T, o = S^T q with f = lower + (1 - lower) sigmoid(zf + b) and q = silu(zq).
-// One CTA per (segment, head, slice of 32 value columns) walks the segment's tokens in order, eight at a time; thread
-// (warp w, lane) keeps rows w * NS .. of column `lane` of the state in registers (float32). For a block of eight tokens
-// the gates, queries and values are computed once into shared memory (their raw projections were fetched into registers
-// while the previous block was applied), then every warp applies the eight tokens to its rows, and the eight warps'
-// partial outputs are added, one token per warp. The state is loaded from the slot at the start (zero at position 0)
-// and stored at the end. o leaves un-normalised, float32.
+// One CTA per (segment, head, slice of 16 value columns) walks the segment's tokens in order, eight at a time; thread
+// (row group w of 16, column c of 16) keeps rows w * NS .. of column c of the state in registers (float32). For a block of
+// eight tokens the gates, queries and values are computed once into shared memory (their raw projections were fetched
+// into registers while the previous block was applied), then every thread applies the eight tokens to its rows, and the
+// sixteen row groups' partial outputs are added per (token, column). The state is loaded from the slot at the start
+// (zero at position 0) and stored at the end. o leaves un-normalised, float32.
 template <typename T, int NS>
 __global__ void __launch_bounds__(256)
 hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b, const float* __restrict__ lower,
-                  float* __restrict__ state, float* __restrict__ o, const int* __restrict__ meta, int ntok, int H, int D, int DV) {
+                  float* __restrict__ state, float* __restrict__ o, const int* __restrict__ meta, const int* __restrict__ seg_starts,
+                  int ntok, int H, int D, int DV) {
   pdl_enter();
-  const int i = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
+  // with a list of the segments' first rows the grid has one CTA per segment; without it, one per token, and the CTAs of
+  // tokens that do not open a segment leave at once (a long prompt then pays for thousands of empty CTAs)
+  const int i = seg_starts ? seg_starts[blockIdx.x] : blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 16;
   const TokMeta mt = load_meta(meta, ntok, i);
   if (i != mt.seg_begin) return;
-  constexpr int BT = 8, DP = 8 * NS, R = (BT * DP) / 256;      // tokens per block, padded rows, staged values per thread
+  constexpr int BT = 8, DP = 16 * NS, R = (BT * DP) / 256;     // tokens per block, padded rows, staged values per thread
   __shared__ __align__(16) float sq[BT][DP], sf[BT][DP], sg[BT][DP];
-  __shared__ float sv[BT][32], spart[BT][8][32];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int col = v0 + lane;
+  __shared__ float sv[BT][16], spart[BT][16][16];
+  const int tid = threadIdx.x, c = tid & 15, grp = tid >> 4;
+  const int col = v0 + c;
   const bool live = col < DV;
-  const int d0 = warp * NS;
+  const int d0 = grp * NS;
   float S[NS];
   float* st = state + (((size_t)mt.slot * H + h) * D) * DV;
 #pragma unroll
   for (int k = 0; k < NS; ++k) S[k] = (mt.pos > 0 && live && d0 + k < D) ? st[(size_t)(d0 + k) * DV + col] : 0.f;
   const int HD = H * D;
-  float zq[R], zf[R], zv;
+  float zq[R], zf[R], zv = 0.f;
   auto fetch = [&](int tb) {                               // raw projections of tokens tb .. tb + 7 into registers
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -335,8 +338,10 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b
         zf[r] = to_f(row[HD]);
       }
     }
-    const int t = tb + warp;
-    zv = (t < mt.seg_end && live) ? to_f(p[(size_t)t * ld + 2 * HD + h * DV + col]) : 0.f;
+    if (tid < BT * 16) {
+      const int t = tb + grp;
+      zv = (t < mt.seg_end && live) ? to_f(p[(size_t)t * ld + 2 * HD + h * DV + col]) : 0.f;
+    }
   };
   fetch(mt.seg_begin);
   for (int tb = mt.seg_begin; tb < mt.seg_end; tb += BT) {
@@ -353,12 +358,12 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b
       }
       sq[tt][d] = q; sf[tt][d] = f; sg[tt][d] = gq;
     }
-    sv[warp][lane] = zv;
+    if (tid < BT * 16) sv[grp][c] = zv;
     __syncthreads();
     if (tb + BT < mt.seg_end) fetch(tb + BT);
     const int nb = min(BT, mt.seg_end - tb);
     for (int tt = 0; tt < nb; ++tt) {
-      const float v = sv[tt][lane];
+      const float v = sv[tt][c];
       float p0 = 0.f, p1 = 0.f;                             // two chains: the sum over rows is the long dependency
       const float4* f4 = reinterpret_cast<const float4*>(&sf[tt][d0]);
       const float4* g4 = reinterpret_cast<const float4*>(&sg[tt][d0]);
@@ -371,14 +376,14 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b
         S[4 * k + 2] = f.z * S[4 * k + 2] + gq.z * v;     p0 += S[4 * k + 2] * q.z;
         S[4 * k + 3] = f.w * S[4 * k + 3] + gq.w * v;     p1 += S[4 * k + 3] * q.w;
       }
-      spart[tt][warp][lane] = p0 + p1;
+      spart[tt][grp][c] = p0 + p1;
     }
     __syncthreads();
-    if (warp < nb && live) {
+    if (tid < BT * 16 && grp < nb && live) {                // thread (token grp, column c) adds the sixteen row groups
       float s = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) s += spart[warp][w][lane];
-      o[(size_t)(tb + warp) * H * DV + (size_t)h * DV + col] = s;
+      for (int w = 0; w < 16; ++w) s += spart[grp][w][c];
+      o[(size_t)(tb + grp) * H * DV + (size_t)h * DV + col] = s;
     }
   }
   if (live) {
@@ -573,30 +578,30 @@ extern "C" int qspec_seq_window_attention(const qspec_window_attn_args* a, int d
 }
 
 template <typename T>
-static int launch_hgrn2(const void* p, int ld, const float* f_b, const float* lower, float* state, float* o, const int* meta, int ntok,
-                        int H, int D, int DV, cudaStream_t st) {
-  const dim3 grid(ntok, H, (DV + 31) / 32);
-#define HG_ARGS dim3(256), 0, st, (const T*)p, ld, f_b, lower, state, o, meta, ntok, H, D, DV
-  if (D <= 32) launch_pdl(hgrn2_scan_kernel<T, 4>, grid, HG_ARGS);
-  else if (D <= 64) launch_pdl(hgrn2_scan_kernel<T, 8>, grid, HG_ARGS);
-  else if (D <= 128) launch_pdl(hgrn2_scan_kernel<T, 16>, grid, HG_ARGS);
-  else launch_pdl(hgrn2_scan_kernel<T, 32>, grid, HG_ARGS);
+static int launch_hgrn2(const void* p, int ld, const float* f_b, const float* lower, float* state, float* o, const int* meta,
+                        const int* seg_starts, int nseg, int ntok, int H, int D, int DV, cudaStream_t st) {
+  const dim3 grid(seg_starts ? nseg : ntok, H, (DV + 15) / 16);
+#define HG_ARGS dim3(256), 0, st, (const T*)p, ld, f_b, lower, state, o, meta, seg_starts, ntok, H, D, DV
+  if (D <= 64) launch_pdl(hgrn2_scan_kernel<T, 4>, grid, HG_ARGS);
+  else if (D <= 128) launch_pdl(hgrn2_scan_kernel<T, 8>, grid, HG_ARGS);
+  else launch_pdl(hgrn2_scan_kernel<T, 16>, grid, HG_ARGS);
 #undef HG_ARGS
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
 }
 
 extern "C" int qspec_seq_hgrn2(const void* p, int ld, const float* f_b, const float* lower, const float* norm_w, float* state,
-                               float* scratch, void* out, const int* meta, int ntok, int H, int D, int DV, float eps, int dtype,
-                               void* stream) {
+                               float* scratch, void* out, const int* meta, const int* seg_starts, int nseg, int ntok, int H, int D,
+                               int DV, float eps, int dtype, void* stream) {
+  QSPEC_REQUIRE(!seg_starts || (nseg >= 1 && nseg <= ntok) || ntok == 0, QSPEC_ERR_INVALID_ARG, "seq_hgrn2: %d segments for %d tokens", nseg, ntok);
   QSPEC_REQUIRE(p && f_b && lower && norm_w && state && scratch && out && meta, QSPEC_ERR_INVALID_ARG, "seq_hgrn2: null pointer");
-  QSPEC_REQUIRE(ntok >= 0 && H > 0 && H <= 65535 && D > 0 && D <= 256 && DV > 0 && DV <= 65535 * 32 && ld >= 2 * H * D + H * DV,
+  QSPEC_REQUIRE(ntok >= 0 && H > 0 && H <= 65535 && D > 0 && D <= 256 && DV > 0 && DV <= 65535 * 16 && ld >= 2 * H * D + H * DV,
                 QSPEC_ERR_UNSUPPORTED, "seq_hgrn2: %d heads, key size %d (<= 256), value size %d", H, D, DV);
   MIX_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  int s = dtype == QSPEC_DTYPE_F32 ? launch_hgrn2<float>(p, ld, f_b, lower, state, scratch, meta, ntok, H, D, DV, st)
-                                   : launch_hgrn2<bf16_t>(p, ld, f_b, lower, state, scratch, meta, ntok, H, D, DV, st);
+  int s = dtype == QSPEC_DTYPE_F32 ? launch_hgrn2<float>(p, ld, f_b, lower, state, scratch, meta, seg_starts, nseg, ntok, H, D, DV, st)
+                                   : launch_hgrn2<bf16_t>(p, ld, f_b, lower, state, scratch, meta, seg_starts, nseg, ntok, H, D, DV, st);
   if (s) return s;
   const long long rows = (long long)ntok * H;
   const unsigned blocks = (unsigned)((rows + 3) / 4);

@@ -443,12 +443,14 @@ class PitudraModel(torch.nn.Module):
             ops.seq_window_attention(qf.view(T, m.heads, m.dim), None, k4, v4, att, tab, m.window, m.scale, sink=p.sink, gate=gate)
         return att.view(T, HDV)
 
-    def _hgrn2(self, i, m, p, h, tab, T):
+    def _hgrn2(self, i, m, p, h, meta, T):
+        tab = meta.table
         ld = m.heads * (2 * m.dim + m.vdim)
         proj = self.buf_proj[:T * ld].view(T, ld)
         torch.matmul(h, p.qfv.t(), out=proj)
         att = self.buf_att[:T * m.heads * m.vdim].view(T, m.heads * m.vdim)
-        ops.seq_hgrn2(proj, p.f_b, p.lower, p.o_norm, self.rec_state[i], self.buf_rec, att, tab, m.heads, m.dim, m.vdim, self.cfg.eps)
+        ops.seq_hgrn2(proj, p.f_b, p.lower, p.o_norm, self.rec_state[i], self.buf_rec, att, tab, m.heads, m.dim, m.vdim, self.cfg.eps,
+                      seg_starts=meta.seg_starts)
         return att
 
     @torch.no_grad()
@@ -472,7 +474,7 @@ class PitudraModel(torch.nn.Module):
             elif m.kind == "attention":
                 att = self._attention(i, m, p, h, tab, T, prompt_shaped)
             else:
-                att = self._hgrn2(i, m, p, h, tab, T)
+                att = self._hgrn2(i, m, p, h, meta, T)
             torch.matmul(att, p.o.t(), out=y)
             more = f is not None or cfg.side_dim > 0                                # a later sublayer of this layer reads x
             ops.seq_add_norm(y, p.norm1, p.norm1_b, eps, x_in=x, x_out=x, out=h if more else None)

@@ -51,6 +51,7 @@ class BatchMeta:
     table: torch.Tensor
     ids: torch.Tensor                                  # device int32 [ntok]: the step's token ids (zeros if none were given)
     rows: torch.Tensor                                 # device int32 [n]: batch rows the caller asked to have gathered
+    seg_starts: torch.Tensor                           # device int32 [segments]: batch row of every segment's first token
     ntok: int
     segments: List[Tuple[Hashable, int, int, int]]     # (request id, slot, first position, token count)
 
@@ -120,7 +121,7 @@ class SequenceTable:
         if len(set(slots)) != len(slots):
             raise ValueError("a request appears twice in one step")
         begin = np.cumsum(counts) - counts
-        h = np.zeros((META_ROWS + 2, ntok), dtype=np.int32)
+        h = np.zeros((META_ROWS + 3, ntok), dtype=np.int32)
         h[0] = np.repeat(np.asarray(slots, dtype=np.int64), counts)
         h[2] = np.repeat(begin, counts)
         h[1] = np.repeat(np.asarray(firsts, dtype=np.int64), counts) + (np.arange(ntok) - h[2])
@@ -132,11 +133,13 @@ class SequenceTable:
         if rows is not None and len(rows):
             nrows = len(rows)
             h[META_ROWS + 1, :nrows] = np.asarray(rows, dtype=np.int64)
+        h[META_ROWS + 2, :len(counts)] = begin         # one entry per segment (a segment has at least one token)
         t = torch.from_numpy(h)
         if self.device.type == "cuda":
             t = t.pin_memory()
         dev = t.to(self.device, non_blocking=True)
-        return BatchMeta(table=dev[:META_ROWS], ids=dev[META_ROWS], rows=dev[META_ROWS + 1, :nrows], ntok=ntok, segments=segs)
+        return BatchMeta(table=dev[:META_ROWS], ids=dev[META_ROWS], rows=dev[META_ROWS + 1, :nrows],
+                         seg_starts=dev[META_ROWS + 2, :len(segs)], ntok=ntok, segments=segs)
 
     def commit(self, meta: BatchMeta) -> None:
         """The step described by `meta` has been queued: its tokens now count as consumed."""

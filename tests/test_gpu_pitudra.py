@@ -334,8 +334,9 @@ def test_hgrn2_state_over_portions_and_slots(dtype, H, D, DV):
     for n in [1, 2, 8, 1, 9, 17, 7]:
         rows = torch.cat([proj[at:at + n], other[at:at + n]]).to(dtype).cuda()
         out = torch.empty(2 * n, H * DV, dtype=dtype, device="cuda")
+        starts = torch.tensor([0, n], dtype=torch.int32, device="cuda") if n % 2 else None      # both grid forms
         ops.seq_hgrn2(rows, sd["f.b"].float().cuda(), sd["lower"].float().cuda(), sd["norm"].float().cuda(), state, scratch, out,
-                      meta_table([(2, at, n, 0), (0, at, n, 0)]), H, D, DV, eps)
+                      meta_table([(2, at, n, 0), (0, at, n, 0)]), H, D, DV, eps, seg_starts=starts)
         got.append(out[:n].float().cpu()); got_other.append(out[n:].float().cpu())
         at += n
     close(torch.cat(got), want, dtype)

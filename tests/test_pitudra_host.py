@@ -102,3 +102,13 @@ def test_sink_softmax_weights():
     w = O.windowed_sink_softmax(s, torch.tensor([0.0], dtype=torch.float64), 2)
     assert torch.allclose(w[0, 0], torch.tensor([0.5, 0, 0, 0], dtype=torch.float64))
     assert torch.allclose(w[0, 3], torch.tensor([0, 0, 1 / 3, 1 / 3], dtype=torch.float64))
+
+
+def test_step_table_lists_the_segments_first_rows():
+    from qspec_b200.state import SequenceTable
+    t = SequenceTable(4, "cpu", 64)
+    m = t.plan([("a", 5), ("b", 1), ("c", 7)], list(range(13)))
+    assert m.seg_starts.tolist() == [0, 5, 6] and m.table[2].tolist() == [0] * 5 + [5] + [6] * 7
+    t.commit(m)
+    m = t.plan([("b", 3)])
+    assert m.seg_starts.tolist() == [0] and m.pos.tolist() == [1, 2, 3]
