@@ -978,7 +978,7 @@ struct WinMma {
 // STREAM: key rows are loaded inside the product loop instead of a whole step ahead (long keys: the fragments of a step
 // would not fit the register file); blockIdx.z selects a slice of DV value columns (values longer than DV).
 template <int DA, int DB, int DV, bool STREAM>
-__global__ void __launch_bounds__(128, STREAM ? 3 : 2) window_attn_mma_kernel(const WinMma a) {
+__global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a) {
   pdl_enter();
   constexpr int DK = DA + DB, QS = DK / 2 + 4;
   extern __shared__ __align__(16) unsigned char wm_raw[];
