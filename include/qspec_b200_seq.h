@@ -164,7 +164,7 @@ int qspec_seq_qkv_prep(const void* p, int ld, int HD, int GD, int GDV, const flo
  * float32 with free token / head strides (elements). Key of (slot, position j, key/value head g) lies at
  * k + slot * k_slot_stride + (j % cap) * k_row_stride + g * k_head_stride, values likewise (a latent cache passes the
  * same buffer twice with G = 1). Query head h uses key/value head h / (H / G). gate (may be NULL): the output is
- * multiplied by sigmoid(gate[t, h * DV + d]). out [ntok, H, DV]. sink may be NULL (no sink). DV <= 512. */
+ * multiplied by sigmoid(gate[t, h * DV + d]). out [ntok, H, DV]. sink may be NULL (no sink). DV <= 1024. */
 typedef struct qspec_window_attn_args {
   const float* qa; long long qa_tok_stride, qa_head_stride; int DA;
   const float* qb; long long qb_tok_stride, qb_head_stride; int DB;
@@ -188,7 +188,7 @@ int qspec_seq_window_attention_mma_supported(int DA, int DB, int DV, int H, int 
 /* HGRN2 recurrence. Row t of p = [zq (H x D) | zf (H x D) | v (H x DV)]. q = silu(zq), f = lower + (1 - lower) *
  * sigmoid(zf + f_b); per head S <- diag(f) S + (1 - f) v^T, o = S^T q; out[t, h] = unit_rms(o over DV) * norm_w.
  * state: float32 [slots, H, D, DV], read at a segment's start (zero at position 0), written at its end.
- * scratch: float32 [ntok, H * DV]. D <= 256. seg_starts (may be NULL): int32 [nseg], the batch row of every segment's
+ * scratch: float32 with room for ntok * H * (DV + 3 D) values (un-normalised outputs and the gates). D <= 256. seg_starts (may be NULL): int32 [nseg], the batch row of every segment's
  * first token; with it the grid has one CTA per segment instead of one per token. */
 int qspec_seq_hgrn2(const void* p, int ld, const float* f_b, const float* lower, const float* norm_w, float* state,
                     float* scratch, void* out, const int* meta, const int* seg_starts, int nseg, int ntok, int H, int D, int DV,

@@ -450,14 +450,14 @@ def _pitudra_kernel_table(torch, s, hbm_gbs, bf16_tflops):
         ldr = H * 3 * D
         pr = [(torch.randn(T, ldr, device=dev)).to(bf) for _ in range(nbuf)]
         state = torch.zeros(nslots, H, D, D, device=dev)
-        scr = torch.empty(T * H * D, device=dev)
+        scr = torch.empty(T * H * 4 * D, device=dev)
         orec = torch.empty(T, H * D, device=dev, dtype=bf)
         fb, lo = torch.zeros(H * D, device=dev), torch.full((H * D,), 0.5, device=dev)
         starts = tab[2].unique().to(torch.int32).contiguous()
         us = _time_us(torch, [lambda i=i: ops.seq_hgrn2(pr[i], fb, lo, wv[:D].contiguous(), state, scr, orec, tab, H, D, D, 1e-5, seg_starts=starts)
                               for i in range(nbuf)])
         nseg = len(segs)
-        add("seq_hgrn2 (scan + head norm)", f"{label} T={T} H={H} D={D}", us,
+        add("seq_hgrn2 (gates + scan + head norm)", f"{label} T={T} H={H} D={D}", us,
             nbytes=T * (ldr * 2 + H * D * 10) + (2 * nseg * H * D * D * 4 if label == "decode" else 0), flops=4.0 * T * H * D * D,
             note="sequential over a sequence's tokens: H x DV/16 CTAs per sequence" if label == "prompt" else None)
         # router and experts

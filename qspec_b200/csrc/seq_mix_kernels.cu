@@ -295,26 +295,45 @@ window_attn_kernel(const float* __restrict__ qa, long long qa_ts, long long qa_h
   }
 }
 
+// ---- HGRN2 gates: q = silu(zq), f = lower + (1 - lower) sigmoid(zf + b), and 1 - f, float32, once per (token, row) -------
+// gates [ntok][3][H * D]. 1 - f = (1 - lower) / (1 + e^z) is formed without the cancellation of 1 - f near f = 1.
+template <typename T>
+__global__ void __launch_bounds__(256)
+hgrn2_gates_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b, const float* __restrict__ lower,
+                   float* __restrict__ gates, int HD, long long n) {
+  pdl_enter();
+  for (long long k = (long long)blockIdx.x * 256 + threadIdx.x; k < n; k += (long long)gridDim.x * 256) {
+    const long long t = k / HD;
+    const int c = (int)(k - t * HD);
+    const T* row = p + (size_t)t * ld;
+    const float zq = to_f(row[c]), z = to_f(row[HD + c]) + f_b[c], lo = lower[c];
+    const float om = 1.0f / (1.0f + expf(z));             // 1 - sigmoid(z)
+    float* g = gates + (size_t)t * 3 * HD + c;
+    g[0] = zq / (1.0f + expf(-zq));
+    g[HD] = lo + (1.0f - lo) * (1.0f - om);
+    g[2 * HD] = (1.0f - lo) * om;
+  }
+}
+
 // ---- HGRN2: gated linear recurrence ---------------------------------------------------------------------------------
 // Per head S <- diag(f) S + (1 - f) v^T, o = S^T q with f = lower + (1 - lower) sigmoid(zf + b) and q = silu(zq).
-// One CTA per (segment, head, slice of 16 value columns) walks the segment's tokens in order, eight at a time; thread
+// One CTA per (segment, head, slice of 16 value columns) walks the segment's tokens in order, 16 (or 8) at a time; thread
 // (row group w of 16, column c of 16) keeps rows w * NS .. of column c of the state in registers (float32). For a block of
-// eight tokens the gates, queries and values are computed once into shared memory (their raw projections were fetched
-// into registers while the previous block was applied), then every thread applies the eight tokens to its rows, and the
+// tokens the gates, queries (hgrn2_gates_kernel) and values are copied into shared memory (they were fetched into
+// registers while the previous block was applied), then every thread applies the block's tokens to its rows, and the
 // sixteen row groups' partial outputs are added per (token, column). The state is loaded from the slot at the start
 // (zero at position 0) and stored at the end. o leaves un-normalised, float32.
-template <typename T, int NS>
+template <typename T, int NS, int BT>
 __global__ void __launch_bounds__(256)
-hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b, const float* __restrict__ lower,
-                  float* __restrict__ state, float* __restrict__ o, const int* __restrict__ meta, const int* __restrict__ seg_starts,
-                  int ntok, int H, int D, int DV) {
+hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ gates, float* __restrict__ state, float* __restrict__ o,
+                  const int* __restrict__ meta, const int* __restrict__ seg_starts, int ntok, int H, int D, int DV) {
   pdl_enter();
   // with a list of the segments' first rows the grid has one CTA per segment; without it, one per token, and the CTAs of
   // tokens that do not open a segment leave at once (a long prompt then pays for thousands of empty CTAs)
   const int i = seg_starts ? seg_starts[blockIdx.x] : blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 16;
   const TokMeta mt = load_meta(meta, ntok, i);
   if (i != mt.seg_begin) return;
-  constexpr int BT = 8, DP = 16 * NS, R = (BT * DP) / 256;     // tokens per block, padded rows, staged values per thread
+  constexpr int DP = 16 * NS, R = (BT * DP) / 256;           // BT tokens per block; padded rows; staged values per thread
   __shared__ __align__(16) float sq[BT][DP], sf[BT][DP], sg[BT][DP];
   __shared__ float sv[BT][16], spart[BT][16][16];
   const int tid = threadIdx.x, c = tid & 15, grp = tid >> 4;
@@ -326,16 +345,15 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b
 #pragma unroll
   for (int k = 0; k < NS; ++k) S[k] = (mt.pos > 0 && live && d0 + k < D) ? st[(size_t)(d0 + k) * DV + col] : 0.f;
   const int HD = H * D;
-  float zq[R], zf[R], zv = 0.f;
-  auto fetch = [&](int tb) {                               // raw projections of tokens tb .. tb + 7 into registers
+  float rq[R], rf[R], rg[R], zv = 0.f;
+  auto fetch = [&](int tb) {                               // gates and values of the block's tokens into registers
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int e = tid + 256 * r, tt = e / DP, d = e % DP, t = tb + tt;
-      zq[r] = 0.f; zf[r] = 0.f;
+      rq[r] = 0.f; rf[r] = 1.f; rg[r] = 0.f;
       if (t < mt.seg_end && d < D) {
-        const T* row = p + (size_t)t * ld + h * D + d;
-        zq[r] = to_f(row[0]);
-        zf[r] = to_f(row[HD]);
+        const float* g = gates + (size_t)t * 3 * HD + h * D + d;
+        rq[r] = g[0]; rf[r] = g[HD]; rg[r] = g[2 * HD];
       }
     }
     if (tid < BT * 16) {
@@ -348,15 +366,7 @@ hgrn2_scan_kernel(const T* __restrict__ p, int ld, const float* __restrict__ f_b
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int e = tid + 256 * r, tt = e / DP, d = e % DP;
-      float q = 0.f, f = 1.f, gq = 0.f;
-      if (d < D) {
-        const float lo = lower[h * D + d], z = zf[r] + f_b[h * D + d];
-        q = zq[r] / (1.0f + expf(-zq[r]));
-        const float om = 1.0f / (1.0f + expf(z));           // 1 - sigmoid(z)
-        gq = (1.0f - lo) * om;                              // 1 - f
-        f = lo + (1.0f - lo) * (1.0f - om);
-      }
-      sq[tt][d] = q; sf[tt][d] = f; sg[tt][d] = gq;
+      sq[tt][d] = rq[r]; sf[tt][d] = rf[r]; sg[tt][d] = rg[r];
     }
     if (tid < BT * 16) sv[grp][c] = zv;
     __syncthreads();
@@ -556,15 +566,16 @@ static int launch_window_attn_n(const qspec_window_attn_args* a, cudaStream_t st
   if (per <= 2) return launch_window_attn<T, 2, VEC>(a, st);
   if (per <= 4) return launch_window_attn<T, 4, VEC>(a, st);
   if (per <= 8) return launch_window_attn<T, 8, VEC>(a, st);
-  return launch_window_attn<T, 16, VEC>(a, st);
+  if (per <= 16) return launch_window_attn<T, 16, VEC>(a, st);
+  return launch_window_attn<T, 32, VEC>(a, st);
 }
 
 extern "C" int qspec_seq_window_attention(const qspec_window_attn_args* a, int dtype, void* stream) {
   QSPEC_REQUIRE(a && a->qa && a->k && a->v && a->out && a->meta && (a->DB == 0 || a->qb), QSPEC_ERR_INVALID_ARG,
                 "seq_window_attention: null pointer");
-  QSPEC_REQUIRE(a->ntok >= 0 && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->DA > 0 && a->DB >= 0 && a->DV > 0 && a->DV <= 512 &&
+  QSPEC_REQUIRE(a->ntok >= 0 && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->DA > 0 && a->DB >= 0 && a->DV > 0 && a->DV <= 1024 &&
                     a->DA + a->DB <= 8192 && a->window >= 1 && a->cap >= 1 && a->H <= 65535,
-                QSPEC_ERR_UNSUPPORTED, "seq_window_attention: heads %d / %d, key size %d + %d (<= 8192), value size %d (<= 512)", a->H,
+                QSPEC_ERR_UNSUPPORTED, "seq_window_attention: heads %d / %d, key size %d + %d (<= 8192), value size %d (<= 1024)", a->H,
                 a->G, a->DA, a->DB, a->DV);
   MIX_DTYPE_OK(dtype);
   if (a->ntok == 0) return QSPEC_OK;
@@ -578,13 +589,21 @@ extern "C" int qspec_seq_window_attention(const qspec_window_attn_args* a, int d
 }
 
 template <typename T>
-static int launch_hgrn2(const void* p, int ld, const float* f_b, const float* lower, float* state, float* o, const int* meta,
+static int launch_hgrn2(const void* p, int ld, const float* f_b, const float* lower, float* state, float* o, float* gates, const int* meta,
                         const int* seg_starts, int nseg, int ntok, int H, int D, int DV, cudaStream_t st) {
+  const long long n = (long long)ntok * H * D;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_pdl(hgrn2_gates_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, st, (const T*)p, ld, f_b, lower, gates, H * D, n);
+  QSPEC_CHECK_LAUNCH(1);
   const dim3 grid(seg_starts ? nseg : ntok, H, (DV + 15) / 16);
-#define HG_ARGS dim3(256), 0, st, (const T*)p, ld, f_b, lower, state, o, meta, seg_starts, ntok, H, D, DV
-  if (D <= 64) launch_pdl(hgrn2_scan_kernel<T, 4>, grid, HG_ARGS);
-  else if (D <= 128) launch_pdl(hgrn2_scan_kernel<T, 8>, grid, HG_ARGS);
-  else launch_pdl(hgrn2_scan_kernel<T, 16>, grid, HG_ARGS);
+#define HG_ARGS dim3(256), 0, st, (const T*)p, ld, (const float*)gates, state, o, meta, seg_starts, ntok, H, D, DV
+  // blocks of 16 tokens for prompt portions (fewer barriers and copies per token); 8 for decoding steps, where the state's
+  // way in and out of the registers is the work and the smaller shared-memory footprint keeps more CTAs on an SM
+  const bool longs = seg_starts && ntok >= 16 * nseg;
+  if (D <= 64) { if (longs) launch_pdl(hgrn2_scan_kernel<T, 4, 16>, grid, HG_ARGS); else launch_pdl(hgrn2_scan_kernel<T, 4, 8>, grid, HG_ARGS); }
+  else if (D <= 128) { if (longs) launch_pdl(hgrn2_scan_kernel<T, 8, 16>, grid, HG_ARGS); else launch_pdl(hgrn2_scan_kernel<T, 8, 8>, grid, HG_ARGS); }
+  else launch_pdl(hgrn2_scan_kernel<T, 16, 8>, grid, HG_ARGS);
 #undef HG_ARGS
   QSPEC_CHECK_LAUNCH(1);
   return QSPEC_OK;
@@ -600,8 +619,9 @@ extern "C" int qspec_seq_hgrn2(const void* p, int ld, const float* f_b, const fl
   MIX_DTYPE_OK(dtype);
   if (ntok == 0) return QSPEC_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  int s = dtype == QSPEC_DTYPE_F32 ? launch_hgrn2<float>(p, ld, f_b, lower, state, scratch, meta, seg_starts, nseg, ntok, H, D, DV, st)
-                                   : launch_hgrn2<bf16_t>(p, ld, f_b, lower, state, scratch, meta, seg_starts, nseg, ntok, H, D, DV, st);
+  float* gates = scratch + (size_t)ntok * H * DV;          // scratch: un-normalised outputs, then the gates
+  int s = dtype == QSPEC_DTYPE_F32 ? launch_hgrn2<float>(p, ld, f_b, lower, state, scratch, gates, meta, seg_starts, nseg, ntok, H, D, DV, st)
+                                   : launch_hgrn2<bf16_t>(p, ld, f_b, lower, state, scratch, gates, meta, seg_starts, nseg, ntok, H, D, DV, st);
   if (s) return s;
   const long long rows = (long long)ntok * H;
   const unsigned blocks = (unsigned)((rows + 3) / 4);

@@ -1077,14 +1077,14 @@ def seq_window_attention_mma(q: torch.Tensor, cache_k: torch.Tensor, k_shared: O
 def seq_hgrn2(p: torch.Tensor, f_b: torch.Tensor, lower: torch.Tensor, norm_w: torch.Tensor, state: torch.Tensor, scratch: torch.Tensor,
               out: torch.Tensor, meta: torch.Tensor, H: int, D: int, DV: int, eps: float, seg_starts: Optional[torch.Tensor] = None) -> None:
     """HGRN2 recurrence over rows [zq | zf | v] with the per-slot state float32 [slots, H, D, DV]; out [ntok, H * DV] after the
-    per-head norm; scratch float32 with room for [ntok, H * DV]. seg_starts: int32, the batch row of every segment's first
+    per-head norm; scratch float32 with room for ntok * H * (DV + 3 D) values. seg_starts: int32, the batch row of every segment's first
     token (`BatchMeta.seg_starts`): one CTA per segment instead of one per token."""
     _chk(seg_starts, "seg_starts", (torch.int32,), allow_none=True)
     _chk(p, "p", _SEQ_ACT); _chk(out, "out", (p.dtype,)); _chk(state, "state", (_F32,)); _chk(scratch, "scratch", (_F32,))
     for t, n in ((f_b, "f_b"), (lower, "lower"), (norm_w, "norm_w")):
         _chk(t, n, (_F32,))
     ntok = p.shape[0]
-    if out.shape != (ntok, H * DV) or state.shape[1:] != (H, D, DV) or scratch.numel() < ntok * H * DV or norm_w.numel() != DV \
+    if out.shape != (ntok, H * DV) or state.shape[1:] != (H, D, DV) or scratch.numel() < ntok * H * (DV + 3 * D) or norm_w.numel() != DV \
             or f_b.numel() != H * D or lower.numel() != H * D:
         raise ValueError("seq_hgrn2: shapes do not match")
     _seq(_lib.load_seq().qspec_seq_hgrn2(_ptr(p), p.shape[1], _ptr(f_b), _ptr(lower), _ptr(norm_w), _ptr(state), _ptr(scratch), _ptr(out),

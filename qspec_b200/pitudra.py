@@ -313,7 +313,7 @@ class PitudraModel(torch.nn.Module):
         self.buf_qa = torch.empty(T * mx([m.heads * (max(m.kv_rank, m.dim) + m.rot_dim) for m in lat] + [m.heads * m.dim for m in att]), **f32)
         self.buf_att = torch.empty(T * mx([m.heads * m.kv_rank for m in lat] + [m.heads * m.vdim for m in att + rec]), **act)
         self.buf_att2 = torch.empty(T * mx(m.heads * m.vdim for m in lat), **act)
-        self.buf_rec = torch.empty(T * mx(m.heads * m.vdim for m in rec), **f32)
+        self.buf_rec = torch.empty(T * mx(m.heads * (m.vdim + 3 * m.dim) for m in rec), **f32)   # un-normalised outputs + gates
         moes = [l.mlp for l in cfg.layers if l.mlp]
         tops = mx(f.top for f in moes)
         self.buf_idx = torch.empty(T * tops, dtype=torch.int32, device=dev)

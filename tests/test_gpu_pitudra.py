@@ -168,7 +168,7 @@ def _run_window_attention(q, k, v, sink, window, scale, G, cuts, dtype, step_cap
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("H,G,DK,DV,window,split", [(4, 2, 16, 8, 7, None), (3, 1, 20, 12, 5, 14), (2, 2, 9, 5, 3, None),
-                                                     (6, 3, 64, 128, 40, None), (2, 1, 66, 40, 1, 64), (5, 1, 130, 300, 16, 120)])
+                                                     (6, 3, 64, 128, 40, None), (2, 1, 66, 40, 1, 64), (5, 1, 130, 300, 16, 120), (1, 1, 700, 690, 9, 690)])
 def test_window_attention_over_portions_and_ring_wraps(dtype, H, G, DK, DV, window, split):
     """Portions that start, end and span ring wraps and window edges; prompt portions and single tokens; the first tokens of a
     sequence (fewer keys than the window); with and without an output gate."""
@@ -329,7 +329,7 @@ def test_hgrn2_state_over_portions_and_slots(dtype, H, D, DV):
     other = rnd(g, T, n_in, dtype=dtype)
     want_other = O.hgrn2(other, sd, "", m, eps)
     state = torch.full((3, H, D, DV), float("nan"), dtype=F32, device="cuda")
-    scratch = torch.empty(2 * T * H * DV, dtype=F32, device="cuda")
+    scratch = torch.empty(2 * T * H * (DV + 3 * D), dtype=F32, device="cuda")
     at, got, got_other = 0, [], []
     for n in [1, 2, 8, 1, 9, 17, 7]:
         rows = torch.cat([proj[at:at + n], other[at:at + n]]).to(dtype).cuda()
