@@ -249,8 +249,13 @@ class PitudraModel(torch.nn.Module):
 
     architecture = "Pitudra"
 
+    RING_ROWS_UNBOUNDED = 32768     # rings longer than this are cut to the sequence limit, if the caller gives one
+
     def __init__(self, cfg: PitudraConfig, weights: Dict[str, torch.Tensor], dtype=torch.bfloat16, device="cuda",
-                 n_slots: int = 8, max_step_tokens: int = 2048):
+                 n_slots: int = 8, max_step_tokens: int = 2048, max_seq_tokens: Optional[int] = None):
+        """max_seq_tokens: the most tokens a sequence will ever hold, if known. It only matters for windows so long that a
+        ring of window - 1 + max_step_tokens rows would be wasteful: such rings get max_seq_tokens rows (positions then never
+        wrap) and the model refuses longer sequences (`max_seq_len`, checked by the scheduler)."""
         super().__init__()
         if dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("PitudraModel: dtype must be torch.bfloat16 or torch.float32")
@@ -280,18 +285,27 @@ class PitudraModel(torch.nn.Module):
         self.cache_v: Dict[int, torch.Tensor] = {}
         self.rec_state: Dict[int, torch.Tensor] = {}
         self.inv_freq: Dict[int, torch.Tensor] = {}
+        self.max_seq_len = None                        # set when a ring is cut to the caller's sequence limit
+
+        def ring_rows(window: int) -> int:
+            rows = window - 1 + T
+            if rows > self.RING_ROWS_UNBOUNDED and max_seq_tokens:
+                rows = min(rows, max(int(max_seq_tokens), T))
+                self.max_seq_len = rows if self.max_seq_len is None else min(self.max_seq_len, rows)
+            return rows
+
         for i, l in enumerate(cfg.layers):
             m = l.mixer
             if m.kind == "latent_attention":
                 if m.kv_from is None:
                     # the ring must hold the widest window of any layer that reads it
                     win = max([m.window] + [o.mixer.window for o in cfg.layers if o.mixer.kv_from == i])
-                    self.latent_cache[i] = torch.zeros(n_slots, win - 1 + T, m.kv_rank + m.rot_dim, **act)
+                    self.latent_cache[i] = torch.zeros(n_slots, ring_rows(win), m.kv_rank + m.rot_dim, **act)
                 half = m.rot_dims // 2
                 f = torch.tensor(m.rot_base, dtype=torch.float64) ** (-2.0 * torch.arange(half, dtype=torch.float64) / max(m.rot_dims, 1))
                 self.inv_freq[i] = f.to(**f32)
             elif m.kind == "attention":
-                cap = m.window - 1 + T
+                cap = ring_rows(m.window)
                 self.cache_k[i] = torch.zeros(n_slots, cap, m.kv_heads * m.dim, **act)
                 self.cache_v[i] = torch.zeros(n_slots, cap, m.kv_heads * m.vdim, **act)
             else:

@@ -59,13 +59,14 @@ def _load_mutusun(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: i
     return MutusunModel.from_pretrained(path, dtype=dt, device=device, n_slots=n_slots, max_step_tokens=max_step_tokens)
 
 
-def _load_pitudra(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: int = 2048, **_):
+def _load_pitudra(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: int = 2048, max_seq_tokens=None, **_):
     import torch
     from .pitudra import PitudraModel
     dt = {"bfloat16": torch.bfloat16, "float32": torch.float32, None: torch.bfloat16}.get(dtype)
     if dt is None:
         raise ValueError(f"Pitudra runs in bfloat16 or float32, not {dtype}")
-    return PitudraModel.from_pretrained(path, dtype=dt, device=device, n_slots=n_slots, max_step_tokens=max_step_tokens)
+    return PitudraModel.from_pretrained(path, dtype=dt, device=device, n_slots=n_slots, max_step_tokens=max_step_tokens,
+                                        max_seq_tokens=max_seq_tokens)
 
 
 def _load_qspec_llama(path, cfg, dtype, device, n_slots: int = 8, max_step_tokens: int = 256, **_):

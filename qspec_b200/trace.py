@@ -40,7 +40,7 @@ def main(argv=None) -> int:
         print("no CUDA device: this framework has no CPU path", file=sys.stderr)
         return 2
     model = registry.load_model(args.model, dtype=args.dtype, device="cuda", n_slots=args.slots,
-                                max_step_tokens=args.step_tokens)
+                                max_step_tokens=args.step_tokens, max_seq_tokens=args.max_tokens or None)
     sched = Scheduler(model)
     os.makedirs(args.out, exist_ok=True)
     for line in sys.stdin:

@@ -578,6 +578,24 @@ def test_prompt_and_decode_forms_on_the_tensor_cores_match_the_plain_implementat
     close_logits(torch.cat(rows), ref[:90], BF16)
 
 
+def test_windows_longer_than_any_sequence_take_rings_of_the_sequence_limit():
+    """A window of ten million positions: with a sequence limit the rings hold that many rows (positions never wrap) and the
+    scheduler refuses a longer sequence; the logits are those of the plain implementation."""
+    _cuda()
+    from qspec_b200.pitudra import PitudraConfig, PitudraModel, random_weights
+    from qspec_b200.scheduler import Scheduler
+    cfg = config([dict(latent(window=10 ** 7), mlp=moe()), dict(attention(window=10 ** 7), mlp=None), dict(latent(window=5, kv_from=0), mlp=None)])
+    w = random_weights(PitudraConfig.from_dict(cfg), 2)
+    model = PitudraModel(PitudraConfig.from_dict(cfg), w, dtype=F32, device="cuda", n_slots=2, max_step_tokens=16, max_seq_tokens=90)
+    assert model.latent_cache[0].shape[1] == 90 and model.cache_k[1].shape[1] == 90 and model.max_seq_len == 90
+    s = Scheduler(model)
+    toks = tokens(90, cfg["vocab"], 4)
+    rows = [s.feed([("a", toks[:50], list(range(50)))])] + [s.feed([("a", [t], [0])]) for t in toks[50:]]
+    close_logits(torch.cat(rows), O.forward(cfg, w, toks), F32)
+    with pytest.raises(RuntimeError):
+        s.feed([("a", [1], [0])])
+
+
 def test_batch_composition_changes_nothing_in_float32():
     cfg, w, model, s = build("mixed", F32, n_slots=3, max_step_tokens=64)
     a, b = tokens(30, cfg["vocab"], 5), tokens(12, cfg["vocab"], 6)
