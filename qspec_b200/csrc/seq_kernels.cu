@@ -550,23 +550,41 @@ route_kernel(const T* __restrict__ h, const float* __restrict__ rw, const float*
   // four elements per lane and load where the rows allow it, four such loads in flight: the dot products are short and
   // latency-bound (router weights and the token's row both come from the L1 / L2)
   const bool vec = (W & 3) == 0 && ((uintptr_t)rw & 15) == 0 && ((uintptr_t)hp & (4 * sizeof(T) - 1)) == 0;
-  for (int r = warp; r < R; r += 4) {
-    const float* wr = rw + (size_t)r * W;
-    float acc = 0.f;
-    if (vec) {
-      float a4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+  if (vec) {
+    // four router rows of a warp at a time (rows warp, warp + 4, warp + 8, warp + 12 of a group of 16): the token's row is
+    // loaded once per step and four weight loads are in flight; every row keeps its own four partial sums, so the result
+    // is the one of a row-by-row loop
+    for (int r0 = warp; r0 < R; r0 += 16) {
+      float a4[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) a4[u][0] = a4[u][1] = a4[u][2] = a4[u][3] = 0.f;
+#pragma unroll 2
       for (int c = lane * 4; c < W; c += 128) {
-        const float4 wv = *reinterpret_cast<const float4*>(wr + c);
         const VecF<4> hv = ldv<4>(hp + c);
-        a4[0] += wv.x * hv.v[0]; a4[1] += wv.y * hv.v[1]; a4[2] += wv.z * hv.v[2]; a4[3] += wv.w * hv.v[3];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int r = r0 + 4 * u;
+          if (r < R) {
+            const float4 wv = *reinterpret_cast<const float4*>(rw + (size_t)r * W + c);
+            a4[u][0] += wv.x * hv.v[0]; a4[u][1] += wv.y * hv.v[1]; a4[u][2] += wv.z * hv.v[2]; a4[u][3] += wv.w * hv.v[3];
+          }
+        }
       }
-      acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
-    } else {
-      for (int c = lane; c < W; c += 32) acc += wr[c] * to_f(hp[c]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + 4 * u;
+        const float acc = warp_xor_sum((a4[u][0] + a4[u][1]) + (a4[u][2] + a4[u][3]));
+        if (r < R && lane == 0) z[r] = acc;
+      }
     }
-    acc = warp_xor_sum(acc);
-    if (lane == 0) z[r] = acc;
+  } else {
+    for (int r = warp; r < R; r += 4) {
+      const float* wr = rw + (size_t)r * W;
+      float acc = 0.f;
+      for (int c = lane; c < W; c += 32) acc += wr[c] * to_f(hp[c]);
+      acc = warp_xor_sum(acc);
+      if (lane == 0) z[r] = acc;
+    }
   }
   __syncthreads();
   if (warp != 0) return;

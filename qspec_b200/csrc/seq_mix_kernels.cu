@@ -494,7 +494,8 @@ extern "C" int qspec_seq_latent_prep(const void* d, int ld, int q_rank, int kv_r
                                      const float* inv_freq, int rot_dims, void* cq, void* cache, int cap, const int* meta, int ntok,
                                      float eps, int dtype, void* stream) {
   QSPEC_REQUIRE(d && qn_w && cq && meta, QSPEC_ERR_INVALID_ARG, "seq_latent_prep: null pointer");
-  QSPEC_REQUIRE(!cache || (kvn_w && inv_freq), QSPEC_ERR_INVALID_ARG, "seq_latent_prep: a cache needs the key/value norm weight and the frequencies");
+  QSPEC_REQUIRE(!cache || (kvn_w && (inv_freq || rot_dims == 0)), QSPEC_ERR_INVALID_ARG,
+                "seq_latent_prep: a cache needs the key/value norm weight and the frequencies");
   QSPEC_REQUIRE(ntok >= 0 && q_rank > 0 && kv_rank >= 0 && rot_dim >= 0 && rot_dims >= 0 && rot_dims <= rot_dim && rot_dims % 2 == 0 &&
                     cap > 0 && ld >= q_rank + (cache ? kv_rank + rot_dim : 0),
                 QSPEC_ERR_INVALID_ARG, "seq_latent_prep: bad sizes");
