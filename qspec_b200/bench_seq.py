@@ -421,7 +421,7 @@ def _pitudra_kernel_table(torch, s, hbm_gbs, bf16_tflops):
                 k4 = c[:, :, :kvr].unsqueeze(2).expand(nslots, cap, groups, kvr)
                 ops.seq_window_attention_mma(qabs[i % 2], k4, c[:, :, kvr:], k4, olat, tab, win, 0.07, False, sink=sink)
             us = _time_us(torch, [lambda i=i: lat_mma(i) for i in range(2)])
-            add("seq_window_attention_mma, latent absorbed form (16 heads per CTA, values in 128-column slices)",
+            add("seq_window_attention_mma, latent absorbed form (16 heads per CTA, key blocks shared by a cluster)",
                 f"64 seqs x 1, {visible // 64} keys each", us, nbytes=visible * (kvr + rot) * 2)
         # grouped-query attention
         ldq = H * D + 2 * G * D + H * D

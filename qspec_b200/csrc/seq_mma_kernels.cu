@@ -1197,6 +1197,232 @@ __global__ void __launch_bounds__(128, 2) window_attn_mma_kernel(const WinMma a)
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Absorbed latent attention for decode-shaped batches, CTA-level form: the rows of a latent cache are keys ([latent DA |
+// shared rotary part 64]) and values (the latent) at once, and all heads of a token read the same rows. One CTA of 8
+// warps per (token, group of up to 16 heads) walks the window in blocks of 64 keys: warp w multiplies the 16 heads'
+// queries with keys 8 w .. 8 w + 7 of the block (key rows streamed through the product loop), the block's row maxima meet
+// in shared memory (one running maximum per head for the whole CTA), the float32 weights go to shared memory as a
+// two-term bfloat16 split, and then warp w adds the block's 64 keys into its own 64 value columns (the rows straight into
+// the fragments, as above). The scores are computed once, not once per slice of value columns.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int DA>
+__global__ void __launch_bounds__(256) latent_absorbed_mma_kernel(const WinMma a, int nsplit) {
+  pdl_enter();
+  constexpr int DB = 64, DK = DA + DB, QS = DK / 2 + 4, NW = 8, PVW = DA / 64, PS = 36;   // PVW warps own 64 value columns each
+  extern __shared__ __align__(16) unsigned char la_raw[];
+  uint32_t* sQ = reinterpret_cast<uint32_t*>(la_raw);        // [16][QS]
+  uint32_t* sPh = sQ + 16 * QS;                               // [16][PS] weights of the block, high terms (64 keys = 32 words)
+  uint32_t* sPl = sPh + 16 * PS;                              // low terms
+  float* sPart = reinterpret_cast<float*>(sPl + 16 * PS);     // clusters only: [16] maxima | [16] sums | [16][DA] value sums
+  const int rank = blockIdx.z;                                // this CTA takes every nsplit-th block of 64 keys
+  __shared__ float sMax[NW][16], sL[NW][16];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+  const int rep = a.H / a.G, i = blockIdx.x, grp = blockIdx.y;
+  const int slot = a.meta[i], pos = a.meta[a.ntok + i];
+  for (int c = tid; c < 16 * (DK / 2); c += 256) {
+    const int row = c / (DK / 2), w = c - row * (DK / 2);
+    uint32_t val = 0u;
+    if (row < rep) {
+      const float2 f = *reinterpret_cast<const float2*>(a.q + (size_t)i * a.q_ts + (size_t)(grp * rep + row) * a.q_hs + 2 * w);
+      val = pack_bf2(f.x, f.y);
+    }
+    sQ[row * QS + w] = val;
+  }
+  __syncthreads();
+  const int jlo = max(0, pos - a.window + 1), nkeys = pos - jlo + 1;
+  const bf16* kA = a.kA + (size_t)slot * a.kA_ss + (size_t)grp * a.kA_hs;
+  const bf16* kB = a.kB + (size_t)slot * a.kB_ss;
+  const bf16* vb = a.v + (size_t)slot * a.v_ss + (size_t)grp * a.v_hs + 64 * warp;
+  const bool inA = gid < rep, inB = gid + 8 < rep;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  float o[8][4];
+#pragma unroll
+  for (int t = 0; t < 8; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+  // the key row of this thread for the next block is fetched while the current block is weighed and added: its 8-element
+  // pieces for all columns stay in registers (the value accumulators of a warp are only 64 columns wide)
+  uint4 kn[DK / 32];
+  auto fetch_keys = [&](int kb) {
+    const int jj = kb + 8 * warp + gid;
+    const bool ok = jj < nkeys;
+    const int row = ok ? (jlo + jj) % a.cap : 0;
+    const bf16* kp = kA + (size_t)row * a.kA_rs + 8 * tig;
+    const bf16* kq = kB + (size_t)row * a.kB_rs + 8 * tig;
+#pragma unroll
+    for (int j = 0; j < DK / 32; ++j)
+      kn[j] = !ok ? zero4 : __ldg(reinterpret_cast<const uint4*>(j < DA / 32 ? kp + 32 * j : kq + 32 * (j - DA / 32)));
+  };
+  fetch_keys(64 * rank);
+  for (int kb = 64 * rank; kb < nkeys; kb += 64 * nsplit) {
+    // scores of this warp's 8 keys: thread (gid, tig) holds key kb + 8 warp + 2 tig (+1) for heads gid and gid + 8
+    float s[4];
+    {
+      float sp[4][4];                                        // four independent chains over the key's columns
+#pragma unroll
+      for (int u = 0; u < 4; ++u) sp[u][0] = sp[u][1] = sp[u][2] = sp[u][3] = 0.f;
+#pragma unroll
+      for (int j = 0; j < DK / 32; ++j) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int wq = 16 * j + 4 * tig + 2 * half;
+          const uint32_t af[4] = {sQ[gid * QS + wq], sQ[(gid + 8) * QS + wq], sQ[gid * QS + wq + 1], sQ[(gid + 8) * QS + wq + 1]};
+          mma_bf16_16816(sp[(2 * j + half) & 3], af, half ? kn[j].z : kn[j].x, half ? kn[j].w : kn[j].y);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[c] = (sp[0][c] + sp[1][c]) + (sp[2][c] + sp[3][c]);
+    }
+    if (kb + 64 * nsplit < nkeys) fetch_keys(kb + 64 * nsplit);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const bool vis = ((c >> 1) ? inB : inA) && kb + 8 * warp + 2 * tig + (c & 1) < nkeys;
+      s[c] = vis ? s[c] * a.scale : -INFINITY;
+    }
+    float mxA = fmaxf(s[0], s[1]), mxB = fmaxf(s[2], s[3]);
+    mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+    mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1)); mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+    if (tig == 0) { sMax[warp][gid] = mxA; sMax[warp][gid + 8] = mxB; }
+    __syncthreads();
+    float nA = mA, nB = mB;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) { nA = fmaxf(nA, sMax[w][gid]); nB = fmaxf(nB, sMax[w][gid + 8]); }
+    const float cA = nA == -INFINITY ? 1.f : __expf(mA - nA), cB = nB == -INFINITY ? 1.f : __expf(mB - nB);
+    const float bA = nA == -INFINITY ? 0.f : nA, bB = nB == -INFINITY ? 0.f : nB;
+    mA = nA; mB = nB;
+    const float w0 = __expf(s[0] - bA), w1 = __expf(s[1] - bA), w2 = __expf(s[2] - bB), w3 = __expf(s[3] - bB);
+    lA = lA * cA + (w0 + w1);
+    lB = lB * cB + (w2 + w3);
+    uint32_t hi, lo;
+    split_bf2(w0, w1, hi, lo);
+    sPh[gid * PS + 4 * warp + tig] = hi; sPl[gid * PS + 4 * warp + tig] = lo;
+    split_bf2(w2, w3, hi, lo);
+    sPh[(gid + 8) * PS + 4 * warp + tig] = hi; sPl[(gid + 8) * PS + 4 * warp + tig] = lo;
+#pragma unroll
+    for (int t = 0; t < 8; ++t) { o[t][0] *= cA; o[t][1] *= cA; o[t][2] *= cB; o[t][3] *= cB; }
+    __syncthreads();
+    if (warp < PVW) {
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        if (kb + 16 * ks >= nkeys) break;
+        const uint32_t ah[4] = {sPh[gid * PS + 8 * ks + tig], sPh[(gid + 8) * PS + 8 * ks + tig], sPh[gid * PS + 8 * ks + 4 + tig],
+                                sPh[(gid + 8) * PS + 8 * ks + 4 + tig]};
+        const uint32_t al[4] = {sPl[gid * PS + 8 * ks + tig], sPl[(gid + 8) * PS + 8 * ks + tig], sPl[gid * PS + 8 * ks + 4 + tig],
+                                sPl[(gid + 8) * PS + 8 * ks + 4 + tig]};
+        uint4 v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int jj = kb + 16 * ks + 2 * tig + (q & 1) + 8 * (q >> 1);
+          v[q] = jj < nkeys ? __ldg(reinterpret_cast<const uint4*>(vb + (size_t)((jlo + jj) % a.cap) * a.v_rs + 8 * gid)) : zero4;
+        }
+        const uint32_t v0[4] = {v[0].x, v[0].y, v[0].z, v[0].w}, v1[4] = {v[1].x, v[1].y, v[1].z, v[1].w};
+        const uint32_t v2[4] = {v[2].x, v[2].y, v[2].z, v[2].w}, v3[4] = {v[3].x, v[3].y, v[3].z, v[3].w};
+#pragma unroll
+        for (int t = 0; t < 8; ++t) {
+          const uint32_t sel = (t & 1) ? 0x7632u : 0x5410u;
+          const uint32_t b0 = __byte_perm(v0[t >> 1], v1[t >> 1], sel), b1 = __byte_perm(v2[t >> 1], v3[t >> 1], sel);
+          mma_bf16_16816(o[t], ah, b0, b1);
+          mma_bf16_16816(o[t], al, b0, b1);
+        }
+      }
+    }
+    // no barrier here: the next block's weights are written after its own first barrier, which every warp reaches only
+    // after it has finished reading this block's
+  }
+  lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+  lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+  __syncthreads();                              // the last block's maxima have been read
+  if (tig == 0) { sL[warp][gid] = lA; sL[warp][gid + 8] = lB; }
+  __syncthreads();
+  float LA = 0.f, LB = 0.f;
+#pragma unroll
+  for (int w = 0; w < NW; ++w) { LA += sL[w][gid]; LB += sL[w][gid + 8]; }
+  if (nsplit > 1) {
+    // partial results of this CTA into its shared memory; rank 0 merges the cluster's through distributed shared memory
+    if (warp == 0 && tig == 0) { sPart[gid] = mA; sPart[gid + 8] = mB; sPart[16 + gid] = LA; sPart[16 + gid + 8] = LB; }
+    if (warp < PVW) {
+#pragma unroll
+      for (int t = 0; t < 8; ++t)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sPart[32 + (gid + 8 * (c >> 1)) * DA + 64 * warp + 8 * (2 * tig + (c & 1)) + t] = o[t][c];
+    }
+    cluster_sync_all();
+  }
+  if (rank == 0 && warp < PVW) {
+    const uint32_t part = (uint32_t)__cvta_generic_to_shared(sPart);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = gid + 8 * half;
+      if (row >= rep) continue;
+      const int head = grp * rep + row;
+      const float m0 = half ? mB : mA;
+      float M = a.sink ? fmaxf(m0, a.sink[head]) : m0;
+      for (int r = 1; r < nsplit; ++r) M = fmaxf(M, __uint_as_float(ld_dsmem_u32(mapa_shared(part + 4u * (uint32_t)row, (uint32_t)r))));
+      const float f0 = m0 == -INFINITY ? 0.f : __expf(m0 - M);
+      float L = (half ? LB : LA) * f0 + (a.sink ? __expf(a.sink[head] - M) : 0.f);
+      float acc[8][2];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) { acc[t][0] = o[t][2 * half] * f0; acc[t][1] = o[t][2 * half + 1] * f0; }
+      for (int r = 1; r < nsplit; ++r) {
+        const float mr = __uint_as_float(ld_dsmem_u32(mapa_shared(part + 4u * (uint32_t)row, (uint32_t)r)));
+        const float fr = mr == -INFINITY ? 0.f : __expf(mr - M);
+        L += __uint_as_float(ld_dsmem_u32(mapa_shared(part + 4u * (uint32_t)(16 + row), (uint32_t)r))) * fr;
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+#pragma unroll
+          for (int e = 0; e < 2; ++e)
+            acc[t][e] += fr * __uint_as_float(ld_dsmem_u32(
+                             mapa_shared(part + 4u * (uint32_t)(32 + row * DA + 64 * warp + 8 * (2 * tig + e) + t), (uint32_t)r)));
+      }
+      const float inv = 1.0f / L;
+      bf16* orow = a.out + ((size_t)i * a.H + head) * a.out_hs + 64 * warp;
+#pragma unroll
+      for (int t = 0; t < 8; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) orow[8 * (2 * tig + e) + t] = __float2bfloat16_rn(acc[t][e] * inv);
+    }
+  }
+  if (nsplit > 1) cluster_sync_all();              // nobody leaves while its partial results may still be read
+}
+
+template <int DA>
+static int launch_latent_absorbed(const WinMma& a, cudaStream_t st) {
+  // a cluster per (token, head group) only while the grid would otherwise leave SMs empty and the window has blocks to share:
+  // 64 tokens x 1 024 rows, 16 heads: 100 / 69 / 108 us with 1 / 2 / 4 CTAs per token (64 / 128 / 256 CTAs on 148 SMs)
+  int nsplit = 1;
+  while (nsplit < 4 && (long long)a.ntok * a.G * nsplit * 2 <= 148 && a.window >= 128 * nsplit * 2) nsplit *= 2;
+  const size_t smem = (size_t)16 * ((DA + 64) / 2 + 4) * 4 + (size_t)2 * 16 * 36 * 4 + (nsplit > 1 ? (size_t)(32 + 16 * DA) * 4 : 0);
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    QSPEC_CUDA(cudaFuncSetAttribute(latent_absorbed_mma_kernel<DA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.ntok, a.G, nsplit);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (nsplit > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = nsplit;
+    ++na;
+  }
+  if (pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  QSPEC_CUDA(cudaLaunchKernelEx(&cfg, latent_absorbed_mma_kernel<DA>, a, nsplit));
+  QSPEC_CHECK_LAUNCH(1);
+  return QSPEC_OK;
+}
+
 template <int DA, int DB, int DV, bool STREAM>
 static int launch_window_mma(const WinMma& a, int slices, cudaStream_t st) {
   constexpr size_t smem = (size_t)16 * ((DA + DB) / 2 + 4) * 4 + (size_t)4 * 16 * DV * sizeof(float);
@@ -1239,6 +1465,13 @@ int window_attention_mma(const qspec_window_attn_args* p, const void* kB, long l
   a.sink = p->sink; a.gate = (const bf16*)p->gate; a.gate_ld = p->gate_ld;
   a.out = (bf16*)p->out; a.out_hs = DV; a.meta = p->meta; a.ntok = p->ntok; a.H = p->H; a.G = p->G; a.window = p->window; a.cap = p->cap;
   a.scale = p->scale; a.token_rows = token_rows;
+  // a latent cache read in the absorbed form (keys and values are the same rows): the CTA-level kernel; QSPEC_SEQ_LATENT=sliced
+  // keeps the form with one CTA per slice of 128 value columns, for comparison
+  static const bool sliced = [] { const char* v = getenv("QSPEC_SEQ_LATENT"); return v && !strcmp(v, "sliced"); }();
+  if (!sliced && !token_rows && DA >= 256 && DV == DA && p->v == p->k && !p->gate) {
+    if (DA == 512) return launch_latent_absorbed<512>(a, st);
+    return launch_latent_absorbed<256>(a, st);
+  }
   if (DA == 512) return launch_window_mma<512, 64, 128, true>(a, DV / 128, st);
   if (DA == 256) return launch_window_mma<256, 64, 128, true>(a, DV / 128, st);
   if (DB) return launch_window_mma<128, 64, 128, false>(a, 1, st);

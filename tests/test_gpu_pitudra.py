@@ -267,21 +267,26 @@ def test_window_attention_on_the_tensor_cores(token_rows, H, G, DA, DB, DV, wind
         close(torch.cat(got[b]), want[b], BF16)
 
 
-@pytest.mark.parametrize("H,groups,r,R,window", [(16, 1, 256, 64, 37), (32, 2, 512, 64, 20), (5, 1, 256, 64, 1), (3, 1, 512, 64, 70)])
-def test_absorbed_latent_attention_on_the_tensor_cores(H, groups, r, R, window):
+@pytest.mark.parametrize("H,groups,r,R,window,n", [(16, 1, 256, 64, 37, 90), (32, 2, 512, 64, 20, 90), (5, 1, 256, 64, 1, 90),
+                                                   (3, 1, 512, 64, 70, 90), (4, 1, 256, 64, 520, 330), (16, 1, 512, 64, 300, 200)])
+def test_absorbed_latent_attention_on_the_tensor_cores(H, groups, r, R, window, n):
     """The cache rows are keys and values at once ([latent | shared rotary part], value = the latent); all heads read the same
-    rows, 16 heads per CTA, the values in slices of 128 columns. Decoded token by token and in small portions."""
+    rows, 16 heads per CTA. Decoded token by token and in small portions; with a long window and few tokens the blocks of a
+    token's keys are shared by a cluster of 2 or 4 CTAs (some of them without a block while the sequence is short)."""
     _cuda()
     from qspec_b200 import ops
     g = torch.Generator().manual_seed(H + r)
-    n, scale, step_cap = 90, 0.05, 8
+    scale, step_cap = 0.05, 8
     cap = window - 1 + step_cap
     q, c = rnd(g, n, H, r + R, dtype=BF16), rnd(g, n, 1, r + R, dtype=BF16)
     sink = rnd(g, H)
     want = _plain_window_attention(q, c, c[..., :r], sink, window, scale, 1)
     cache = torch.full((3, cap, r + R), 1e4, dtype=BF16, device="cuda")
     at, got = 0, []
-    for k in [1] * 40 + [5, 8, 3, 8, 8, 2, 8, 8]:
+    cuts, pattern = [], [1] * 40 + [5, 8, 3, 8, 8, 2, 8, 8]
+    while sum(cuts) < n:
+        cuts.append(min(pattern[len(cuts) % len(pattern)], n - sum(cuts)))
+    for k in cuts:
         cache[2, [(t % cap) for t in range(at, at + k)]] = c[at:at + k, 0].to(BF16).cuda()
         out = torch.empty(k, H, r, dtype=BF16, device="cuda")
         ck = cache[:, :, :r].unsqueeze(2).expand(3, cap, groups, r)
